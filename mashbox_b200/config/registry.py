@@ -53,10 +53,14 @@ def _builtin():
     if _done:
         return
     _done = True
-    from ..models import llama, luzosun, sufopel
+    from ..models import llama, luzosun, sufopel, tosevik
     from .llama import LlamaConfig
     from .luzosun import LuzosunConfig
     from .sufopel import SufopelConfig
+    from .tosevik import TosevikConfig
+    if "Tosevik" not in ARCHITECTURES:
+        register_architecture(Architecture("Tosevik", TosevikConfig, tosevik.model_spec, tosevik.canonical_names,
+                                           tosevik.stored_tensors))
     if "Sufopel" not in ARCHITECTURES:
         register_architecture(Architecture("Sufopel", SufopelConfig, sufopel.model_spec, sufopel.canonical_names,
                                            sufopel.stored_tensors))

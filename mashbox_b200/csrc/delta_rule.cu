@@ -13,7 +13,8 @@
 //   delta_gates   from the (convolved) q/k/v product and the small products: silu; q and k to unit vectors per head (q
 //                 also times dim^-1/2); beta = sigmoid; g = exp(-exp(A) softplus(a + dt_bias)); all left in float32
 //   delta_rule    the recurrence
-//   gated_rms     o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, to the storage type
+//   gated_rms     o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, to the storage type (w may be absent; the gate
+//                 may be silu(gate) instead)
 #include "common.cuh"
 
 #define DR_THREADS 128
@@ -259,7 +260,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 // grid (N, H): o (N, H vdim) float32 -> out in the storage type
 template <typename T>
 __global__ void gated_rms_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride, int gate_off,
-                                 const float* __restrict__ w, T* __restrict__ out, int H, int vdim, float eps) {
+                                 const float* __restrict__ w, T* __restrict__ out, int H, int vdim, float eps, int silu) {
     __shared__ float scratch[32];
     const int n = blockIdx.x, h = blockIdx.y;
     const float* src = o + ((size_t)n * H + h) * vdim;
@@ -268,8 +269,10 @@ __global__ void gated_rms_kernel(const float* __restrict__ o, const T* __restric
     ss = mb_block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(ss / (float)vdim + eps);
     const T* gp = gate + (size_t)n * gate_stride + gate_off + (size_t)h * vdim;
-    for (int c = threadIdx.x; c < vdim; c += blockDim.x)
-        mb_store(out + ((size_t)n * H + h) * vdim + c, src[c] * r * w[c] * dr_sigmoid(mb_load(gp + c)));
+    for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+        const float z = mb_load(gp + c);
+        mb_store(out + ((size_t)n * H + h) * vdim + c, src[c] * r * (w ? w[c] : 1.0f) * (silu ? dr_silu(z) : dr_sigmoid(z)));
+    }
 }
 
 template <typename T>
@@ -332,21 +335,21 @@ MB_API int mb_delta_rule(const float* q, const float* k, const float* v, const f
 
 template <typename T>
 static int gated_rms_launch(const float* o, const T* gate, int gate_stride, int gate_off, const float* w, T* out, int N,
-                            int H, int vdim, float eps, cudaStream_t st) {
+                            int H, int vdim, float eps, int silu, cudaStream_t st) {
     if (N == 0) return 0;
     if (H < 1 || H > 65535 || vdim < 1) return -2;
     gated_rms_kernel<T><<<dim3(N, H), vdim > 64 ? 128 : vdim > 32 ? 64 : 32, 0, st>>>(o, gate, gate_stride, gate_off, w, out,
-                                                                                     H, vdim, eps);
+                                                                                     H, vdim, eps, silu);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
 MB_API int mb_gated_rms_f32(const float* o, const void* gate, int gate_stride, int gate_off, const float* w, void* out, int N,
-                            int H, int vdim, float eps, cudaStream_t st) {
-    return gated_rms_launch<float>(o, (const float*)gate, gate_stride, gate_off, w, (float*)out, N, H, vdim, eps, st);
+                            int H, int vdim, float eps, int silu, cudaStream_t st) {
+    return gated_rms_launch<float>(o, (const float*)gate, gate_stride, gate_off, w, (float*)out, N, H, vdim, eps, silu, st);
 }
 
 MB_API int mb_gated_rms_bf16(const float* o, const void* gate, int gate_stride, int gate_off, const float* w, void* out, int N,
-                             int H, int vdim, float eps, cudaStream_t st) {
-    return gated_rms_launch<bf16>(o, (const bf16*)gate, gate_stride, gate_off, w, (bf16*)out, N, H, vdim, eps, st);
+                             int H, int vdim, float eps, int silu, cudaStream_t st) {
+    return gated_rms_launch<bf16>(o, (const bf16*)gate, gate_stride, gate_off, w, (bf16*)out, N, H, vdim, eps, silu, st);
 }

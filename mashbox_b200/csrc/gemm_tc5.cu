@@ -30,7 +30,7 @@
 
 // MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M); 3: bf16 out (N, M) =
 // xIELU of the product (ap z^2 + z / 2 for z > 0, an (e^z - 1 - z) + z / 2 otherwise); 4: as 1 with the gate of routed
-// experts, g = min(gate, ap), u = clamp(up, -ap, ap), out = g sigmoid(an g) (u + 1).
+// experts, g = min(gate, ap), u = clamp(up, -ap, ap), out = g sigmoid(an g) (u + shift).
 //
 // Grouped form (tile_expert given): W is a stack of matrices of `expert_rows` rows each, and every tile of 128 rows of
 // act belongs to one of them -- tile_expert[token tile] says which, -1: the tile holds no rows and is passed over by
@@ -40,7 +40,7 @@ template <int MODE>
 __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap amap,
                                                            const __grid_constant__ CUtensorMap wmap,
                                                            void* __restrict__ out, int N, int M, int K, float ap,
-                                                           float an, int* err, const int* __restrict__ tile_expert,
+                                                           float an, float shift, int* err, const int* __restrict__ tile_expert,
                                                            int expert_rows) {
     constexpr bool GATED = MODE == 1 || MODE == 4;
     constexpr int FEATS = GATED ? 128 : 256;              // output features of one tile
@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
                         float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
                         if (MODE == 4) {
                             g = fminf(g, ap);
-                            up = fminf(fmaxf(up, -ap), ap) + 1.0f;
+                            up = fminf(fmaxf(up, -ap), ap) + shift;
                             r[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-an * g)) * up);
                         } else {
                             // fast exponential and division: no slow path for huge or tiny gate values
@@ -206,7 +206,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
 
 template <int MODE>
 static int tc5_launch(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st,
-                      float ap = 0.0f, float an = 0.0f, const int* tile_expert = nullptr, int experts = 1) {
+                      float ap = 0.0f, float an = 0.0f, const int* tile_expert = nullptr, int experts = 1,
+                      float shift = 1.0f) {
     if (N == 0 || M == 0) return 0;
     if (K % 8 || M % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 15))
@@ -232,7 +233,7 @@ static int tc5_launch(const void* act, const void* W, void* out, int N, int M, i
     }
     const int feats = PER == 2 ? 128 : 256;
     const int tiles = ((N + G_BM - 1) / G_BM) * ((M + feats - 1) / feats);
-    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, ap, an, err, tile_expert,
+    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, ap, an, shift, err, tile_expert,
                                                                         PER * M);
     MB_LAUNCH_CHECK();
     return 0;
@@ -261,12 +262,13 @@ MB_API int mb_gemm_tc5_f32out(const void* act, const void* W, void* out, int N, 
 
 // Grouped forms: act (N, K) with N a multiple of 128, every 128 rows one expert's (tile_expert[N / 128]: its index, -1:
 // no rows); W a stack of `experts` matrices.  Gated: (experts, 2 M, K), gate rows then up rows of each expert,
-// out (N, M) bf16 = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+// out (N, M) bf16 = g sigmoid(alpha g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit).
 MB_API int mb_gemm_tc5_grouped_gated_bf16(const void* act, const void* W, void* out, int N, int M, int K,
-                                          const int* tile_expert, int experts, float limit, float alpha, int* err,
+                                          const int* tile_expert, int experts, float limit, float alpha, float shift,
+                                          int* err,
                                           cudaStream_t st) {
     if (!tile_expert) return -2;
-    return tc5_launch<4>(act, W, out, N, M, K, err, st, limit, alpha, tile_expert, experts);
+    return tc5_launch<4>(act, W, out, N, M, K, err, st, limit, alpha, tile_expert, experts, shift);
 }
 // W (experts, M, K); out (N, M) float32
 MB_API int mb_gemm_tc5_grouped_f32out(const void* act, const void* W, void* out, int N, int M, int K, const int* tile_expert,

@@ -32,18 +32,36 @@ __device__ __forceinline__ int warp_argmax(const float* vals, int n, int lane) {
 }
 
 // one warp per token; dynamic shared: s[E], c[E], gs[groups], kept[groups]
-__global__ void moe_select_kernel(const float* __restrict__ z, const float* __restrict__ correction, int* __restrict__ ids,
-                                  float* __restrict__ wts, int E, int top, int groups, int keep) {
+// softmax: the scores are softmax(z) over all experts instead of sigmoid(z); worth_max: a group is worth its largest c
+// instead of the sum of its two largest; scale multiplies the weights; a row of z is z_stride floats long
+__global__ void moe_select_kernel(const float* __restrict__ z, int z_stride, const float* __restrict__ correction,
+                                  int* __restrict__ ids, float* __restrict__ wts, int E, int top, int groups, int keep,
+                                  int softmax, int worth_max, float scale) {
     extern __shared__ float sm[];
     float* s = sm;
     float* c = sm + E;
     float* gs = sm + 2 * E;
     float* kept = gs + groups;
     const int n = blockIdx.x, lane = threadIdx.x;
-    for (int e = lane; e < E; e += 32) {
-        const float v = 1.0f / (1.0f + expf(-z[(size_t)n * E + e]));
-        s[e] = v;
-        c[e] = v + (correction ? correction[e] : 0.0f);
+    const float* zr = z + (size_t)n * z_stride;
+    if (softmax) {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+        m = mb_warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) { const float v = expf(zr[e] - m); s[e] = v; sum += v; }
+        sum = mb_warp_sum(sum);
+        for (int e = lane; e < E; e += 32) {
+            const float v = s[e] / sum;
+            s[e] = v;
+            c[e] = v + (correction ? correction[e] : 0.0f);
+        }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            const float v = 1.0f / (1.0f + expf(-zr[e]));
+            s[e] = v;
+            c[e] = v + (correction ? correction[e] : 0.0f);
+        }
     }
     __syncwarp();
     if (groups > 1 && keep < groups) {
@@ -54,7 +72,7 @@ __global__ void moe_select_kernel(const float* __restrict__ z, const float* __re
                 const float v = c[e];
                 if (v > a) { b = a; a = v; } else if (v > b) b = v;
             }
-            gs[gi] = per > 1 ? a + b : a;
+            gs[gi] = (per > 1 && !worth_max) ? a + b : a;
             kept[gi] = 0.0f;
         }
         __syncwarp();
@@ -73,7 +91,7 @@ __global__ void moe_select_kernel(const float* __restrict__ z, const float* __re
         __syncwarp();
         if (lane == 0) {
             ids[(size_t)n * top + kk] = at;
-            wts[(size_t)n * top + kk] = s[at];
+            wts[(size_t)n * top + kk] = s[at] * scale;
             c[at] = -INFINITY;
         }
         __syncwarp();
@@ -123,7 +141,7 @@ __device__ __forceinline__ float lane_dot(const bf16* w, const float* x, int K, 
 template <typename T>
 __global__ void moe_experts_up_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __restrict__ wg,
                                       const T* __restrict__ wu, long long gu_stride, float* __restrict__ act, int D, int F,
-                                      int E, int top, float limit, float alpha) {
+                                      int E, int top, float limit, float alpha, float shift) {
     extern __shared__ float hx[];
     const int pair = blockIdx.x, j0 = blockIdx.y * MOE_ROWS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -140,7 +158,7 @@ __global__ void moe_experts_up_kernel(const T* __restrict__ h, const int* __rest
         if (lane == 0) {
             g = fminf(g, limit);
             u = fminf(fmaxf(u, -limit), limit);
-            act[(size_t)pair * F + j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+            act[(size_t)pair * F + j] = g / (1.0f + expf(-alpha * g)) * (u + shift);
         }
     }
 }
@@ -164,36 +182,41 @@ __global__ void moe_experts_down_kernel(const float* __restrict__ act, const int
 
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, T* __restrict__ out, int D,
-                                   int top, long long total) {
+                                   int top, long long total, const T* __restrict__ shared, const float* __restrict__ gate,
+                                   int gate_stride) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long n = i / D;
     const int d = (int)(i - n * D);
     float acc = 0.0f;
     for (int kk = 0; kk < top; kk++) acc = fmaf(wts[n * top + kk], y[(n * top + kk) * D + d], acc);
+    // an expert every token uses, times sigmoid of the token's gate logit (no gate: added as it is)
+    if (shared) acc = fmaf(gate ? 1.0f / (1.0f + expf(-gate[n * gate_stride])) : 1.0f, mb_load(shared + i), acc);
     mb_store(out + i, acc);
 }
 
-MB_API int mb_moe_select(const float* z, const float* correction, int* ids, float* wts, int N, int E, int top, int groups,
-                         int keep, cudaStream_t st) {
+MB_API int mb_moe_select(const float* z, int z_stride, const float* correction, int* ids, float* wts, int N, int E, int top,
+                         int groups, int keep, int softmax, int worth_max, float scale, cudaStream_t st) {
     if (N == 0) return 0;
-    if (E < 1 || top < 1 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups || E > 8192) return -2;
+    if (E < 1 || top < 1 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups || E > 8192 || z_stride < E) return -2;
     if ((long long)keep * (E / groups) < top) return -2;
-    moe_select_kernel<<<N, 32, (size_t)(2 * E + 2 * groups) * sizeof(float), st>>>(z, correction, ids, wts, E, top, groups, keep);
+    moe_select_kernel<<<N, 32, (size_t)(2 * E + 2 * groups) * sizeof(float), st>>>(z, z_stride, correction, ids, wts, E, top,
+                                                                                   groups, keep, softmax, worth_max, scale);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
 template <typename T>
 static int moe_experts_launch(const T* h, const int* ids, const T* wg, const T* wu, long long gu_stride, const T* wd, float* y,
-                              float* act, int N, int D, int F, int E, int top, float limit, float alpha, cudaStream_t st) {
+                              float* act, int N, int D, int F, int E, int top, float limit, float alpha, float shift,
+                              cudaStream_t st) {
     if (N == 0) return 0;
     const long long P = (long long)N * top;
     if (D < 1 || F < 1 || top < 1 || P > 0x7fffffff || D > 12000 || F > 12000 || (F + MOE_ROWS - 1) / MOE_ROWS > 65535 ||
         (D + MOE_ROWS - 1) / MOE_ROWS > 65535)
         return -2;
     moe_experts_up_kernel<T><<<dim3((unsigned)P, (F + MOE_ROWS - 1) / MOE_ROWS), 256, (size_t)D * sizeof(float), st>>>(
-        h, ids, wg, wu, gu_stride, act, D, F, E, top, limit, alpha);
+        h, ids, wg, wu, gu_stride, act, D, F, E, top, limit, alpha, shift);
     MB_LAUNCH_CHECK();
     moe_experts_down_kernel<T><<<dim3((unsigned)P, (D + MOE_ROWS - 1) / MOE_ROWS), 256, (size_t)F * sizeof(float), st>>>(
         act, ids, wd, y, D, F, E);
@@ -203,33 +226,37 @@ static int moe_experts_launch(const T* h, const int* ids, const T* wg, const T* 
 
 MB_API int mb_moe_experts_f32(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
                               const void* wd, float* y, float* act, int N, int D, int F, int E, int top, float limit,
-                              float alpha, cudaStream_t st) {
+                              float alpha, float shift, cudaStream_t st) {
     return moe_experts_launch<float>((const float*)h, ids, (const float*)wg, (const float*)wu, gu_stride, (const float*)wd, y,
-                                     act, N, D, F, E, top, limit, alpha, st);
+                                     act, N, D, F, E, top, limit, alpha, shift, st);
 }
 
 MB_API int mb_moe_experts_bf16(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
                                const void* wd, float* y, float* act, int N, int D, int F, int E, int top, float limit,
-                               float alpha, cudaStream_t st) {
+                               float alpha, float shift, cudaStream_t st) {
     return moe_experts_launch<bf16>((const bf16*)h, ids, (const bf16*)wg, (const bf16*)wu, gu_stride, (const bf16*)wd, y, act,
-                                    N, D, F, E, top, limit, alpha, st);
+                                    N, D, F, E, top, limit, alpha, shift, st);
 }
 
 template <typename T>
-static int moe_combine_launch(const float* y, const float* wts, T* out, int N, int D, int top, cudaStream_t st) {
+static int moe_combine_launch(const float* y, const float* wts, T* out, int N, int D, int top, const T* shared,
+                              const float* gate, int gate_stride, cudaStream_t st) {
     if (N == 0) return 0;
     const long long total = (long long)N * D;
-    moe_combine_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(y, wts, out, D, top, total);
+    moe_combine_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(y, wts, out, D, top, total, shared, gate,
+                                                                           gate_stride);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
-MB_API int mb_moe_combine_f32(const float* y, const float* wts, void* out, int N, int D, int top, cudaStream_t st) {
-    return moe_combine_launch<float>(y, wts, (float*)out, N, D, top, st);
+MB_API int mb_moe_combine_f32(const float* y, const float* wts, void* out, int N, int D, int top, const void* shared,
+                              const float* gate, int gate_stride, cudaStream_t st) {
+    return moe_combine_launch<float>(y, wts, (float*)out, N, D, top, (const float*)shared, gate, gate_stride, st);
 }
 
-MB_API int mb_moe_combine_bf16(const float* y, const float* wts, void* out, int N, int D, int top, cudaStream_t st) {
-    return moe_combine_launch<bf16>(y, wts, (bf16*)out, N, D, top, st);
+MB_API int mb_moe_combine_bf16(const float* y, const float* wts, void* out, int N, int D, int top, const void* shared,
+                               const float* gate, int gate_stride, cudaStream_t st) {
+    return moe_combine_launch<bf16>(y, wts, (bf16*)out, N, D, top, (const bf16*)shared, gate, gate_stride, st);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -320,7 +347,8 @@ template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, long long b_stride,
                    const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top,
-                   int Nout, int K, bf16* __restrict__ out_act, float* __restrict__ out_y, float limit, float alpha) {
+                   int Nout, int K, bf16* __restrict__ out_act, float* __restrict__ out_y, float limit, float alpha,
+                   float shift) {
     constexpr int NB = MODE == 0 ? 2 : 1;
     __shared__ __align__(16) bf16 sA[2][GG_TM][GG_LD];
     __shared__ __align__(16) bf16 sB[2][NB][GG_TN][GG_LD];
@@ -400,7 +428,7 @@ moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, cons
                 if (MODE == 0) {
                     const float g = fminf(acc[0][j][half * 2 + x], limit);
                     const float u = fminf(fmaxf(acc[NB - 1][j][half * 2 + x], -limit), limit);
-                    out_act[(size_t)(r0 + r) * Nout + n] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+                    out_act[(size_t)(r0 + r) * Nout + n] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + shift));
                 } else {
                     out_y[(size_t)pair * Nout + n] = acc[0][j][half * 2 + x];
                 }
@@ -412,7 +440,7 @@ moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, cons
 MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
                                const void* wd, float* y,
                                void* act, int* sorted, int* offsets, int* tiles, int* n_tiles, int N, int D, int F, int E,
-                               int top, float limit, float alpha, cudaStream_t st) {
+                               int top, float limit, float alpha, float shift, cudaStream_t st) {
     if (N == 0) return 0;
     const long long P = (long long)N * top;
     if (D % 8 || F % 8 || D < 8 || F < 8 || E < 1 || E > 4096 || P > (1 << 24)) return -2;
@@ -421,11 +449,11 @@ MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, co
     MB_LAUNCH_CHECK();
     moe_grouped_kernel<0><<<dim3(max_tiles, (F + GG_TN - 1) / GG_TN), 128, 0, st>>>(
         (const bf16*)h, (const bf16*)wg, (const bf16*)wu, gu_stride, sorted, tiles, n_tiles, top, F, D, (bf16*)act, nullptr,
-        limit, alpha);
+        limit, alpha, shift);
     MB_LAUNCH_CHECK();
     moe_grouped_kernel<1><<<dim3(max_tiles, (D + GG_TN - 1) / GG_TN), 128, 0, st>>>(
         (const bf16*)act, (const bf16*)wd, nullptr, (long long)D * F, sorted, tiles, n_tiles, top, D, F, nullptr, y, limit,
-        alpha);
+        alpha, shift);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -478,11 +506,14 @@ __global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, const int* __
 }
 
 __global__ void moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ wts,
-                                        bf16* __restrict__ out, int D, int top) {
+                                        bf16* __restrict__ out, int D, int top, const bf16* __restrict__ shared,
+                                        const float* __restrict__ gate, int gate_stride) {
     const int n = blockIdx.x;
+    const float sg = shared ? (gate ? 1.0f / (1.0f + expf(-gate[(size_t)n * gate_stride])) : 1.0f) : 0.0f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.0f;
         for (int kk = 0; kk < top; kk++) acc = fmaf(wts[(size_t)n * top + kk], y[(size_t)place[(size_t)n * top + kk] * D + d], acc);
+        if (shared) acc = fmaf(sg, __bfloat162float(shared[(size_t)n * D + d]), acc);
         out[(size_t)n * D + d] = __float2bfloat16_rn(acc);
     }
 }
@@ -502,9 +533,9 @@ MB_API int mb_moe_sort_gather(const void* h, const int* ids, int* place, int* ti
 }
 
 MB_API int mb_moe_combine_rows(const float* y, const int* place, const float* wts, void* out, int N, int D, int top,
-                               cudaStream_t st) {
+                               const void* shared, const float* gate, int gate_stride, cudaStream_t st) {
     if (N == 0) return 0;
-    moe_combine_rows_kernel<<<N, 256, 0, st>>>(y, place, wts, (bf16*)out, D, top);
+    moe_combine_rows_kernel<<<N, 256, 0, st>>>(y, place, wts, (bf16*)out, D, top, (const bf16*)shared, gate, gate_stride);
     MB_LAUNCH_CHECK();
     return 0;
 }

@@ -395,24 +395,125 @@ def delta_rule_lanes(lanes):
     f(int(lanes))
 
 
-def gated_rms(o, gate, w, out, H, vdim, eps):
-    """out[n, h] = o[n, h] / sqrt(mean(o[n, h]^2) + eps) * w * sigmoid(gate[n, h]); o (N, H vdim) float32, gate a view
-    (N, H vdim) of the activation dtype whose rows may be further apart, w (vdim,) float32, out the activation dtype"""
+def gated_rms(o, gate, w, out, H, vdim, eps, silu=False):
+    """out[n, h] = o[n, h] / sqrt(mean(o[n, h]^2) + eps) * w * sigmoid(gate[n, h]) per head; o (N, H vdim) float32, gate
+    (N, H vdim) of the activation dtype whose rows may be further apart, w (vdim,) float32 or None (no weight), out the
+    activation dtype; silu: the gate is silu(gate) instead of sigmoid(gate)"""
     _cuda(o, gate, w, out)
     f = _fn("delta_rule", "mb_gated_rms_" + _suffix(out.dtype),
-            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
-    _check(f(_p(o), _p(gate), gate.stride(0), 0, _p(w), _p(out), o.shape[0], H, vdim, float(eps), _stream()), "gated_rms")
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_p(o), _p(gate), gate.stride(0), 0, _p(w), _p(out), o.shape[0], H, vdim, float(eps), int(bool(silu)), _stream()),
+           "gated_rms")
+
+
+# ------------------------------------------------------------------------------------------------ the stream of blocks with Dynamic Tanh
+def dyt(x, delta, alpha, w, b, out, rows=None, delta2=None):
+    """x (N, D) float32 += delta (+ delta2) (in place unless rows picks rows); out = tanh(alpha x) * w + b.  out is of
+    the activation dtype (that of delta when given) or float32 -- it may be x itself"""
+    _cuda(x, delta, delta2, w, b, out, rows)
+    D = x.shape[1]
+    n_out = x.shape[0] if rows is None else rows.shape[0]
+    act = delta.dtype if delta is not None else out.dtype
+    out_float = out.dtype == torch.float32 and act != torch.float32
+    f = _fn("stream", "mb_dyt_" + _suffix(act),
+            [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(delta2), float(alpha), _p(w), _p(b), _p(out), int(out_float), _p(rows), n_out, D, _stream()),
+           "dyt")
+
+
+def depth_average(x, delta, hist, coef, idx, normed=None, next_norm=None):
+    """y = x + delta;  hist[idx + 1] = y;  x = sum_(j <= idx + 1) coef[j] hist[j].  x (N, D) float32, delta (N, D) of the
+    activation dtype or None, hist (slots, rows >= N, D) float32, coef (idx + 2,) float32.  With normed and
+    next_norm = (alpha, w, b): normed = tanh(alpha x) * w + b, of the activation dtype."""
+    _cuda(x, delta, hist, coef, normed)
+    N, D = x.shape
+    act = delta.dtype if delta is not None else (normed.dtype if normed is not None else torch.float32)
+    if coef.numel() < idx + 2 or hist.shape[0] < idx + 2 or hist.shape[1] < N:
+        raise KernelError("depth_average: the history or the coefficients are too short")
+    na, nw, nb = next_norm if normed is not None else (0.0, None, None)
+    f = _fn("stream", "mb_depth_average_" + _suffix(act),
+            [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(hist), hist.stride(0), _p(coef), int(idx), float(na), _p(nw), _p(nb), _p(normed), N, D,
+             _stream()), "depth_average")
+
+
+def rms_pair_mean(a, b, wa, wb, out, eps):
+    """out = (a / rms(a) * wa + b / rms(b) * wb) / 2 row by row; a, b, out (N, D) of the activation dtype, wa, wb float32"""
+    _cuda(a, b, wa, wb, out)
+    N, D = a.shape
+    f = _fn("stream", "mb_rms_pair_mean_" + _suffix(a.dtype), [c_void_p] * 5 + [c_int, c_int, c_float, c_void_p])
+    _check(f(_p(a), _p(b), _p(wa), _p(wb), _p(out), N, D, float(eps), _stream()), "rms_pair_mean")
+
+
+# ------------------------------------------------------------------------------------------------ retention
+def retention_prep(rows, q_off, k_off, v_off, positions, freqs, q, k, v, H, dim, vdim, rotary_dim, k_scale):
+    """rows (N, C) of the activation dtype holds q at column q_off, k at k_off (H dim each) and v at v_off (H vdim); the
+    first rotary_dim values of every head of q and k turn by position * freqs[i] (value i with value i + rotary_dim / 2);
+    k is multiplied by k_scale after that; q, k (N, H, dim) and v (N, H, vdim) float32"""
+    _cuda(rows, positions, freqs, q, k, v)
+    f = _fn("retention", "mb_retention_prep_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5
+            + [c_float, c_void_p])
+    _check(f(_p(rows), rows.stride(0), int(q_off), int(k_off), int(v_off), _p(positions), _p(freqs), _p(q), _p(k), _p(v),
+             rows.shape[0], H, dim, vdim, int(rotary_dim), float(k_scale), _stream()), "retention_prep")
+
+
+RETENTION = {"chunk_tokens": 64}        # steps with more tokens than this run the chunk form of the recurrence
+
+
+def retention(q, k, v, decay, o, state, seq, H, dim, vdim, chunked=False):
+    """Per sequence and head, token by token: S <- decay[h] S + k v^T; o = S^T q.  q, k (N, H, dim), v, o (N, H, vdim)
+    float32; decay (H,) float32; state (slots, >= H vdim dim) float32, a head's state stored (vdim, dim);
+    seq = (q_start, q_len, state_slot) device arrays.  chunked: the form that works a stretch of tokens side by side."""
+    _cuda(q, k, v, decay, o, state, *seq)
+    f = _fn("retention", "mb_retention_chunk" if chunked else "mb_retention_scan",
+            [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
+    _check(f(_p(q), _p(k), _p(v), _p(decay), _p(o), _p(state), state.stride(0), _p(seq[0]), _p(seq[1]), _p(seq[2]),
+             seq[0].numel(), H, dim, vdim, _stream()), "retention")
+
+
+# ------------------------------------------------------------------------------------------------ attention with sigmoid weights
+def sigmoid_attention_prep(rows, qw, kw, positions, tok_row, table, q_out, kpool, vpool, H, G, dim, vdim, page, num_pages,
+                           eps, temp_coef, temp_every, err):
+    """rows (N, H dim + G dim + G vdim) = [q | k | v]: q and k divided by the root mean square of their whole row and
+    multiplied by qw, kw (float32, a value per channel), q also by 1 + temp_coef ln(floor((p + 1) / temp_every) + 1)
+    (temp_every 0: no such factor); every head's v divided by its own root mean square.  q goes to q_out (N, H dim), k and
+    v into kpool (pages, G, page, dim) and vpool (pages, G, page, vdim) at the token's position (None: not written)."""
+    _cuda(rows, qw, kw, positions, tok_row, table, q_out, kpool, vpool)
+    f = _fn("attention_sigmoid", "mb_sigattn_prep_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+            + [c_int] * 7 + [c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_p(rows), rows.stride(0), _p(qw), _p(kw), _p(positions), _p(tok_row), _p(table), table.shape[1], _p(q_out),
+             _p(kpool), _p(vpool), rows.shape[0], H, G, dim, vdim, page, num_pages, float(eps), float(temp_coef),
+             int(temp_every), _p(err), _stream()), "sigmoid_attention_prep")
+
+
+def sigmoid_attention_simple(q, out, positions, tok_row, table, kpool, vpool, slopes, bias, H, G, dim, vdim, page, num_pages,
+                             scale, err):
+    """out[n, h] = sum over the keys j <= p of sigmoid(scale q[n, h] . k_j - slopes[h] (p - j) + bias[h]) v_j, one warp per
+    (token, head), keys in ascending position; slopes, bias (H,) float32 or None"""
+    _cuda(q, out, positions, tok_row, table, kpool, vpool, slopes, bias)
+    f = _fn("attention_sigmoid", "mb_sigattn_simple_" + _suffix(q.dtype),
+            [c_void_p] * 5 + [c_int] + [c_void_p] * 4 + [c_int] * 7 + [c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(positions), _p(tok_row), _p(table), table.shape[1], _p(kpool), _p(vpool), _p(slopes),
+             _p(bias), q.shape[0], H, G, dim, vdim, page, num_pages, float(scale), _p(err), _stream()),
+           "sigmoid_attention_simple")
 
 
 # ------------------------------------------------------------------------------------------------ routed experts
-def moe_select(z, correction, ids, wts, groups=1, keep=1):
-    """z (N, E) float32 router logits -> ids (N, top) int32, wts (N, top) float32: scores sigmoid(z); chosen by score +
-    correction among the experts of the `keep` best of `groups` runs of neighbours (a run's worth: its two largest);
-    the weights are the chosen experts' scores"""
+def moe_select(z, correction, ids, wts, groups=1, keep=1, experts=None, softmax=False, worth="top2", scale=1.0):
+    """z (N, >= E) float32 router logits (E = experts, default: every column) -> ids (N, top) int32, wts (N, top) float32:
+    scores sigmoid(z), or softmax(z) over the E experts; chosen by score + correction among the experts of the `keep` best
+    of `groups` runs of neighbours (a run's worth: the sum of its two largest, "top2", or its largest, "max"); the
+    weights are the chosen experts' scores times `scale`"""
     _cuda(z, correction, ids, wts)
-    N, E = z.shape
-    f = _fn("moe", "mb_moe_select", [c_void_p] * 4 + [c_int] * 5 + [c_void_p])
-    _check(f(_p(z), _p(correction), _p(ids), _p(wts), N, E, ids.shape[1], int(groups), int(keep), _stream()), "moe_select")
+    N = z.shape[0]
+    E = int(experts) if experts is not None else z.shape[1]
+    if worth not in ("top2", "max"):
+        raise KernelError(f"moe_select: a group's worth is top2 or max, not {worth!r}")
+    f = _fn("moe", "mb_moe_select", [c_void_p, c_int] + [c_void_p] * 3 + [c_int] * 7 + [c_float, c_void_p])
+    _check(f(_p(z), z.stride(0), _p(correction), _p(ids), _p(wts), N, E, ids.shape[1], int(groups), int(keep),
+             int(bool(softmax)), int(worth == "max"), float(scale), _stream()), "moe_select")
 
 
 def _expert_views(wg, wu, wd):
@@ -421,8 +522,8 @@ def _expert_views(wg, wu, wd):
         raise KernelError("the experts' matrices must have contiguous rows, gate and up alike")
 
 
-def moe_experts(h, ids, wg, wu, wd, y, limit, alpha, act=None):
-    """y[n, k] = Wd[e] (g sigmoid(alpha g) (u + 1)), g = min(Wg[e] h[n], limit), u = clamp(Wu[e] h[n], -limit, limit),
+def moe_experts(h, ids, wg, wu, wd, y, limit, alpha, act=None, shift=1.0):
+    """y[n, k] = Wd[e] (g sigmoid(alpha g) (u + shift)), g = min(Wg[e] h[n], limit), u = clamp(Wu[e] h[n], -limit, limit),
     e = ids[n, k].  h (N, D); wg, wu (E, F, D), whole tensors or the two halves of one (E, 2F, D) tensor; wd (E, D, F);
     y (N, top, D) float32; act (N * top, F) float32: working memory (made here when not given)"""
     _cuda(h, ids, wg, wu, wd, y, act)
@@ -432,9 +533,9 @@ def moe_experts(h, ids, wg, wu, wd, y, limit, alpha, act=None):
     if act is None:
         act = torch.empty((N * ids.shape[1], F), dtype=torch.float32, device=h.device)
     f = _fn("moe", "mb_moe_experts_" + _suffix(h.dtype),
-            [c_void_p] * 4 + [c_ll] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_float, c_void_p])
+            [c_void_p] * 4 + [c_ll] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_float, c_float, c_void_p])
     _check(f(_p(h), _p(ids), _p(wg), _p(wu), wg.stride(0), _p(wd), _p(y), _p(act), N, D, F, E, ids.shape[1], float(limit),
-             float(alpha), _stream()), "moe_experts")
+             float(alpha), float(shift), _stream()), "moe_experts")
     COUNTERS["launches"] += 1
 
 
@@ -452,7 +553,7 @@ def moe_grouped_scratch(N, top, E):
     return P + (E + 1) + 3 * (P // 64 + E) + 1 + 3
 
 
-def moe_grouped(h, ids, wg, wu, wd, y, act, scratch, limit, alpha):
+def moe_grouped(h, ids, wg, wu, wd, y, act, scratch, limit, alpha, shift=1.0):
     """moe_experts for steps of many tokens, bf16: the (token, place) pairs are sorted by expert on the device and every
     expert's rows run through tensor-core tiles.  act (N * top, F) bf16 and scratch (moe_grouped_scratch values, int32)
     are working memory."""
@@ -468,9 +569,9 @@ def moe_grouped(h, ids, wg, wu, wd, y, act, scratch, limit, alpha):
     tiles = scratch[P + E + 1:P + E + 1 + 3 * max_tiles]
     n_tiles = scratch[P + E + 1 + 3 * max_tiles:]
     _expert_views(wg, wu, wd)
-    f = _fn("moe", "mb_moe_grouped_bf16", [c_void_p] * 4 + [c_ll] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_float, c_void_p])
+    f = _fn("moe", "mb_moe_grouped_bf16", [c_void_p] * 4 + [c_ll] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_float, c_float, c_void_p])
     _check(f(_p(h), _p(ids), _p(wg), _p(wu), wg.stride(0), _p(wd), _p(y), _p(act), _p(sorted_), _p(offsets), _p(tiles),
-             _p(n_tiles), N, D, F, E, top, float(limit), float(alpha), _stream()), "moe_grouped")
+             _p(n_tiles), N, D, F, E, top, float(limit), float(alpha), float(shift), _stream()), "moe_grouped")
     COUNTERS["launches"] += 2
 
 
@@ -484,11 +585,12 @@ def moe_tc5_tiles(N, top, E):
     return N * top // 128 + E
 
 
-def moe_tc5(h, ids, wts, wgu, wd, out, rows, act, y, scratch, limit, alpha):
+def moe_tc5(h, ids, wts, wgu, wd, out, rows, act, y, scratch, limit, alpha, shift=1.0, shared=None, gate=None):
     """The routed experts of a step of many tokens, bf16: ids (N, top) and wts from moe_select; wgu (E, 2F, D), every
     expert's gate rows then its up rows; wd (E, D, F); out (N, D).  Working memory, with T = moe_tc5_tiles(N, top, E):
-    rows (128 T, D) bf16, act (128 T, F) bf16, y (128 T, D) float32, scratch (N top + T) int32."""
-    _cuda(h, ids, wts, wgu, wd, out, rows, act, y, scratch)
+    rows (128 T, D) bf16, act (128 T, F) bf16, y (128 T, D) float32, scratch (N top + T) int32.  shared (N, D) and gate
+    (float32, one logit per token, rows gate.stride(0) apart): see moe_combine."""
+    _cuda(h, ids, wts, wgu, wd, out, rows, act, y, scratch, shared, gate)
     N, D = h.shape
     E, F = wgu.shape[0], wgu.shape[1] // 2
     top = ids.shape[1]
@@ -500,25 +602,29 @@ def moe_tc5(h, ids, wts, wgu, wd, out, rows, act, y, scratch, limit, alpha):
     _check(f(_p(h), _p(ids), _p(place), _p(tile_expert), _p(rows), N, D, E, top, _stream()), "moe_sort_gather")
     err = error_word(h.device)
     f = _fn("gemm_tc5", "mb_gemm_tc5_grouped_gated_bf16",
-            [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
-    _check(f(_p(rows), _p(wgu), _p(act), 128 * T, F, D, _p(tile_expert), E, float(limit), float(alpha), _p(err), _stream()),
+            [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(rows), _p(wgu), _p(act), 128 * T, F, D, _p(tile_expert), E, float(limit), float(alpha), float(shift), _p(err),
+             _stream()),
            "gemm_tc5_grouped_gated")
     f = _fn("gemm_tc5", "mb_gemm_tc5_grouped_f32out", [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_p(act), _p(wd), _p(y), 128 * T, D, F, _p(tile_expert), E, _p(err), _stream()), "gemm_tc5_grouped")
-    f = _fn("moe", "mb_moe_combine_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
-    _check(f(_p(y), _p(place), _p(wts), _p(out), N, D, top, _stream()), "moe_combine_rows")
+    f = _fn("moe", "mb_moe_combine_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_p(y), _p(place), _p(wts), _p(out), N, D, top, _p(shared), _p(gate), gate.stride(0) if gate is not None else 0,
+             _stream()), "moe_combine_rows")
     COUNTERS["launches"] += 1
 
 
-def moe_combine(y, wts, out):
-    """out[n] = sum_k wts[n, k] y[n, k] (places in order); y (N, top, D) float32, out (N, D) the activation dtype"""
-    _cuda(y, wts, out)
+def moe_combine(y, wts, out, shared=None, gate=None):
+    """out[n] = sum_k wts[n, k] y[n, k] (places in order); y (N, top, D) float32, out (N, D) the activation dtype.
+    shared (N, D) of the activation dtype: the output of an expert every token uses, added times sigmoid(gate[n]) (gate:
+    float32, one logit per token, rows gate.stride(0) apart; None: added as it is)"""
+    _cuda(y, wts, out, shared, gate)
     N, top, D = y.shape
-    f = _fn("moe", "mb_moe_combine_" + _suffix(out.dtype), [c_void_p] * 3 + [c_int] * 3 + [c_void_p])
-    _check(f(_p(y), _p(wts), _p(out), N, D, top, _stream()), "moe_combine")
+    f = _fn("moe", "mb_moe_combine_" + _suffix(out.dtype), [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_p(y), _p(wts), _p(out), N, D, top, _p(shared), _p(gate), gate.stride(0) if gate is not None else 0, _stream()),
+           "moe_combine")
 
 
-# ------------------------------------------------------------------------------------------------ contractions
 def linear(a, w, out=None, out_dtype=None):
     """a (N, K) @ w (M, K)^T -> (N, M).  float32: the package's own fixed-order FFMA kernel (no TF32, no tensor
     cores).  bfloat16: cuBLAS with float accumulation; out_dtype float32 keeps the accumulator's precision."""

@@ -38,6 +38,9 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "rowwise": ("rowwise.cu", []),                                     # learned positions, norms of sublayer outputs, latents
     "delta_rule": ("delta_rule.cu", []),                               # the gated delta rule and what feeds it
     "moe": ("moe.cu", []),                                             # routed experts
+    "stream": ("stream.cu", []),                                       # Dynamic Tanh, depth averaging, two normed outputs
+    "retention": ("retention.cu", []),                                 # linear attention with a fixed decay per head
+    "attention_sigmoid": ("attention_sigmoid.cu", []),                 # attention whose weights are sigmoids
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),

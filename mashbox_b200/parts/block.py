@@ -4,6 +4,9 @@
 sublayer returns its output as `pending` and the next norm adds it into the float32 residual stream in the same kernel
 that normalises, so the block returns the feed-forward's output still pending.
 
+"prenorm_depth": "prenorm", after which the stream is replaced by a weighted sum of everything it has been so far (see
+DepthAveragedBlock).
+
 "sandwich": a norm before AND after each sublayer, the normed output scaled per channel before it joins the stream,
 and optionally an input from the token itself at the layer's end (see SandwichBlock).
 """
@@ -50,6 +53,81 @@ class PreNormBlock:
 
 
 register("block", "prenorm", PreNormBlock)
+
+
+class DepthAveragedBlock:
+    """y = x + mixer(norm1(x));  y += ffn(norm2(y));  X_(index+1) = y;  x = sum_(j <= index+1) c[j] X_j.
+
+    X_0 is the stream as the embedding left it and X_(j+1) the result of the block with `index` j, before this sum; the
+    block with index i reads i + 2 coefficients from the tensor `coef` under its prefix.  The history is one workspace
+    buffer (`total` + 1 slots of the step's rows, float32).  One kernel adds the feed-forward's output, writes the
+    history slot, sums, writes the stream and -- when the norm that reads the stream next works element by element
+    (`elementwise()`) -- makes that norm's output too.  `ffn` may be None.  Nothing is left pending."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, prefix, mixer, norm, index, total, ffn=None, coef="dwa", names=None):
+        n = dict(norm1="norm1", norm2="norm2")
+        n.update(names or {})
+        self.index, self.total = int(index), int(total)
+        if not 0 <= self.index < self.total:
+            raise ConfigError(f"a depth-averaged block with index {index} of {total}")
+        self.norm1 = make("norm", norm, name=prefix + n["norm1"])
+        self.mixer = make("mixer", mixer, prefix=prefix)
+        self.ffn = make("feed_forward", ffn, prefix=prefix) if ffn is not None else None
+        self.norm2 = make("norm", norm, name=prefix + n["norm2"]) if self.ffn is not None else None
+        self.coef_name = prefix + coef
+        self.width = self.norm1.width
+        self.coef = None
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self) if p is not None]
+
+    # the block is a part of its own for the coefficients
+    def wants(self):
+        from ..weights.loader import Want
+        return [Want(self.coef_name, (self.index + 2,), "vector")]
+
+    def bind(self, tensors, env):
+        self.coef = tensors[self.coef_name]
+
+    def first_norm(self):
+        return self.norm1
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def prepare(self, ctx):
+        self.mixer.prepare(ctx)
+
+    def forward(self, ctx, x, pending, run):
+        import torch
+        ctx.after_norm = None
+        hist = ctx.ws.get("depth_history", self.total + 1, (ctx.ws.max_rows, self.width), torch.float32,
+                          reserve=self.total + 1)
+        ready = ctx.memo.pop("prenormed", None)
+        if pending is None and ready is not None and ready[0] is self.norm1 and ready[1] == x.data_ptr():
+            h = ready[2]                    # the block before made this norm while it wrote the stream
+        else:
+            h = self.norm1.forward(ctx, x, pending)
+        if self.index == 0:
+            hist[0, :x.shape[0]].copy_(x)   # the stream as the embedding left it (what was pending is in by now)
+        pending = self.mixer.forward(ctx, h, run)
+        if self.ffn is not None:
+            pending = self.ffn.forward(ctx, self.norm2.forward(ctx, x, pending))
+        delta, bias = pending
+        if bias is not None:
+            raise ConfigError("a depth-averaged block cannot defer a bias")
+        nxt = ctx.next_first_norm
+        if not (nxt is not None and hasattr(nxt, "elementwise") and nxt.width == self.width):
+            nxt = None
+        normed = ctx.ws.get("normed", x.shape[0], (self.width,), ctx.dtype) if nxt is not None else None
+        ctx.ops.depth_average(x, delta, hist, self.coef, self.index, normed, nxt.elementwise() if nxt is not None else None)
+        if nxt is not None:
+            ctx.memo["prenormed"] = (nxt, x.data_ptr(), normed)
+        return None
+
+
+register("block", "prenorm_depth", DepthAveragedBlock)
 
 
 class ParallelBlock:

@@ -1,7 +1,7 @@
 """Token embedding (rows gathered into the float32 residual stream, src/mashbox/gguf/archs/dense.py:328-329) and the
 output head (logits = h W^T in float32; the head is the embedding table when the model ties them, dense.py:129, 390)."""
 from ..weights.loader import Want
-from .base import register
+from .base import make, register
 
 
 class Embedding:
@@ -45,6 +45,28 @@ class PositionedEmbedding(Embedding):
                                 self.scale)
 
 
+class NormedEmbedding(Embedding):
+    """x = norm(table[token] * scale): the token's row goes through a norm of the model's kind (`norm`: its spec) on its
+    way into the stream.  The norm must be one that works element by element and can write the float32 stream in place
+    (`forward(..., out=)`)."""
+    graph_safe = True
+
+    def __init__(self, vocab, hidden, norm, name="token_embd.weight", scale=1.0):
+        super().__init__(vocab, hidden, name, scale)
+        self.norm = make("norm", norm)
+
+    def wants(self):
+        return super().wants() + self.norm.wants()
+
+    def bind(self, tensors, env):
+        super().bind(tensors, env)
+        self.norm.bind(tensors, env)
+
+    def forward(self, ctx, x):
+        super().forward(ctx, x)
+        self.norm.forward(ctx, x, None, out=x)
+
+
 class LinearHead:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, vocab, hidden, tied, name="output.weight", tied_to="token_embd.weight", scale=1.0):
@@ -70,4 +92,5 @@ class LinearHead:
 
 register("embedding", "table", Embedding)
 register("embedding", "table_positions", PositionedEmbedding)
+register("embedding", "table_normed", NormedEmbedding)
 register("head", "linear", LinearHead)

@@ -26,7 +26,9 @@ class SwiGLU:
 
     fuses_small = True      # forward() takes normed= and residual= (see PreNormBlock)
 
-    def forward(self, ctx, h, normed=None, residual=None):
+    def forward(self, ctx, h, normed=None, residual=None, out="delta"):
+        """out: the workspace buffer the result is left in (a part that runs this one beside something else names
+        another one than the default)"""
         import torch
         N = ctx.N
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
@@ -43,7 +45,7 @@ class SwiGLU:
         if residual is not None:
             ctx.add_into_stream(a, self.wd, residual)
             return None
-        y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
+        y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)
         return y, None
 

@@ -63,3 +63,43 @@ class RMSNorm:
 
 
 register("norm", "rms", RMSNorm)
+
+
+class DynamicTanh:
+    """y = tanh(alpha v) * w + b, element by element: no mean, no variance, no eps.  alpha is one number, w and b are
+    vectors, stored as `<name>.alpha`, `<name>` and `<name>.b`; v is the residual stream plus what is pending, as in
+    RMSNorm.  `eps` is accepted and not used, so that a model can hand every norm the same parameters."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, width, name, eps=None):
+        self.width, self.name = int(width), name
+        self.alpha = self.weight = self.bias = None
+
+    def wants(self):
+        return [Want(self.name, (self.width,), "vector"), Want(self.name + ".b", (self.width,), "vector"),
+                Want(self.name + ".alpha", (), "vector")]
+
+    def bind(self, tensors, env):
+        self.weight, self.bias = tensors[self.name], tensors[self.name + ".b"]
+        self.alpha = float(tensors[self.name + ".alpha"].float().cpu())
+
+    def elementwise(self):
+        """(alpha, w, b) for a kernel that makes this norm's output while it writes the stream"""
+        return self.alpha, self.weight, self.bias
+
+    def forward(self, ctx, x, pending=None, rows=None, out=None):
+        """out: where the result goes (default: the workspace's buffer of normed rows); it may be x itself"""
+        n_out = x.shape[0] if rows is None else rows.shape[0]
+        if out is None:
+            out = ctx.ws.get("normed" if rows is None else "normed_rows", n_out, (self.width,), ctx.dtype,
+                             reserve=None if rows is None else ctx.options.get("logit_rows", 8))
+        delta, bias, *more = pending if pending is not None else (None, None)
+        if bias is not None:
+            raise ConfigError("a Dynamic Tanh norm cannot take a pending bias")
+        if delta is not None:
+            ctx.memo.pop("held", None)
+        ctx.ops.dyt(x, delta, self.alpha, self.weight, self.bias, out, rows, more[0] if more else None)
+        return out
+
+
+register("norm", "dyt", DynamicTanh)

@@ -19,15 +19,18 @@ def tensor_seed(seed, name):
 
 
 def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, norm_std=0.01, std_by_name=()):
-    """shapes: {name: (shape, kind)} with kind "matrix" | "norm" | "bias" -> {name: tensor of dtype on device}.
+    """shapes: {name: (shape, kind)} with kind "matrix" | "norm" | "bias" | "alpha" (one number about 1) | "depth" (the
+    coefficients of a weighted average) -> {name: tensor of dtype on device}.
     std_by_name: (substring, std) pairs; the first whose substring is in a matrix's or bias's name replaces std."""
     out = {}
     for name, (shape, kind) in shapes.items():
         g = torch.Generator(device=device)
         g.manual_seed(tensor_seed(seed, name))
         x = torch.randn(tuple(shape), generator=g, device=device, dtype=torch.float32)
-        if kind == "norm":
+        if kind in ("norm", "alpha"):
             x = 1.0 + norm_std * x
+        elif kind == "depth":               # coefficients of a weighted average: about 1 / their number each
+            x = 1.0 / max(1, x.numel()) + norm_std * x
         else:
             x = next((s for sub, s in std_by_name if sub in name), std) * x
         out[name] = x.to(dtype)
