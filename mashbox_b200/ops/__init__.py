@@ -500,6 +500,52 @@ def sigmoid_attention_simple(q, out, positions, tok_row, table, kpool, vpool, sl
            "sigmoid_attention_simple")
 
 
+SIGMOID_MMA_ROWS, SIGMOID_DECODE_ROWS, SIGMOID_MAX_SPLITS = 64, 16, 16
+
+
+def sigmoid_attention_mma_supports(dim, vdim):
+    """the tensor-core kernel of the attention with sigmoid weights takes these head sizes (bfloat16 only)"""
+    return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def _sigmoid_mma_library(dim, vdim):
+    from .build import variant
+    return variant(f"attention_sigmoid_mma_{dim}_{vdim}", "attention_sigmoid_mma.cu", [f"-DSIG_DIM={dim}", f"-DSIG_VD={vdim}"])
+
+
+def sigmoid_attention_mma(q, out, items, n_items, q_start, q_len, pos0, seq_row, table, kpool, vpool, slopes, bias, H, G, dim,
+                          vdim, page, num_pages, scale, err):
+    """Attention with sigmoid weights on tensor cores (bfloat16): the same result as sigmoid_attention_simple.  items:
+    n_items (sequence, tile of 64 packed rows) pairs; q_start, q_len, pos0, seq_row per sequence.  The kernel is compiled
+    for the pair (dim, vdim) the first time it is asked for."""
+    _cuda(q, out, items, q_start, q_len, pos0, seq_row, table, kpool, vpool, slopes, bias)
+    if q.dtype != torch.bfloat16 or not sigmoid_attention_mma_supports(dim, vdim):
+        raise KernelError(f"sigmoid_attention_mma: no kernel for {q.dtype} with head sizes {dim} and {vdim}")
+    f = _fn(_sigmoid_mma_library(dim, vdim), "mb_sigattn_mma", [c_void_p] * 5 + [c_int] + [c_void_p] * 5 + [c_int]
+            + [c_void_p] * 2 + [c_int] * 4 + [c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(kpool), _p(vpool), _p(items), int(n_items), _p(q_start), _p(q_len), _p(pos0), _p(seq_row),
+             _p(table), table.shape[1], _p(slopes), _p(bias), H, G, page, num_pages, float(scale), _p(err), _stream()),
+           "sigmoid_attention_mma")
+
+
+def sigmoid_attention_mma_decode(q, out, items, n_items, slots, n_slots, part_o, q_start, q_len, pos0, seq_row, table, kpool,
+                                 vpool, slopes, bias, H, G, dim, vdim, page, num_pages, scale, err):
+    """The decode form of sigmoid_attention_mma, for sequences of at most 16 packed rows: items are n_items (sequence,
+    split, number of splits, slot) quadruples, the keys of a sequence cut into splits that run side by side; slots:
+    n_slots (sequence, number of splits) pairs of the sequences that are cut, whose partial sums a second kernel adds in
+    the order of the splits from part_o (n_slots * G * 16 * 16, vdim) float32."""
+    _cuda(q, out, items, slots, part_o, q_start, q_len, pos0, seq_row, table, kpool, vpool, slopes, bias)
+    if q.dtype != torch.bfloat16 or not sigmoid_attention_mma_supports(dim, vdim):
+        raise KernelError(f"sigmoid_attention_mma_decode: no kernel for {q.dtype} with head sizes {dim} and {vdim}")
+    f = _fn(_sigmoid_mma_library(dim, vdim), "mb_sigattn_mma_decode", [c_void_p] * 5 + [c_int, c_void_p, c_int]
+            + [c_void_p] * 6 + [c_int] + [c_void_p] * 2 + [c_int] * 4 + [c_float, c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(kpool), _p(vpool), _p(items), int(n_items), _p(slots), int(n_slots), _p(part_o),
+             _p(q_start), _p(q_len), _p(pos0), _p(seq_row), _p(table), table.shape[1], _p(slopes), _p(bias), H, G, page,
+             num_pages, float(scale), _p(err), _stream()), "sigmoid_attention_mma_decode")
+    if n_slots:
+        COUNTERS["launches"] += 1
+
+
 # ------------------------------------------------------------------------------------------------ routed experts
 def moe_select(z, correction, ids, wts, groups=1, keep=1, experts=None, softmax=False, worth="top2", scale=1.0):
     """z (N, >= E) float32 router logits (E = experts, default: every column) -> ids (N, top) int32, wts (N, top) float32:

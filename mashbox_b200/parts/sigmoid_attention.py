@@ -11,11 +11,19 @@
 `slopes` are one number per query head (a model hands them in; `geometric_slopes(heads, 8)` gives 2^(-8 (h+1) / heads)).
 A position's cache row is a key of (kv_heads, dim) and a value of (kv_heads, vdim), both after their norms.  Norms,
 scores, weights and sums are float32.
+
+Kernels: the float32 path, and head sizes that are no multiples of 16 up to 128, use the plain kernel (a warp per token
+and head, keys in ascending order).  The bfloat16 path packs the query heads of a kv head into the rows of an MMA tile:
+tiles of 64 rows for prompt portions, tiles of 16 with the keys split over warps and over blocks for decode tokens;
+`prepare` builds both work lists on the host.  A weight reaches the second product as two bfloat16 numbers (hi + lo).
 """
+import numpy as np
+
 from ..cache.manager import CacheNeed
 from ..errors import ConfigError
 from ..weights.loader import Want
 from .base import register
+from .diff_attention import plan_diff_attention
 
 
 def geometric_slopes(heads, span=8.0):
@@ -68,8 +76,32 @@ class SigmoidAttention:
     def state_need(self):
         return None
 
+    def uses_mma(self, ctx):
+        import torch
+        return (ctx.dtype == torch.bfloat16 and ctx.ops.sigmoid_attention_mma_supports(self.dim, self.vdim)
+                and not ctx.options.get("plain_attention", False))
+
+    def plan_key(self):
+        # everything the work lists depend on (layers with the same grouping of heads share them)
+        return ("sigmoid_attention", self.H // self.G, self.G)
+
     def prepare(self, ctx):
-        pass
+        """host side, for the tensor-core kernels: the lists of (sequence, row tile) work items of the prompt form and
+        of (sequence, split, splits, slot) items of the decode form"""
+        if not self.uses_mma(ctx):
+            return
+        key = self.plan_key()
+        if key in ctx.memo:
+            return
+        ops = ctx.ops
+        name = "sig%d_" % len([k for k in ctx.memo if k[0] == "sigmoid_attention"])
+        plan = plan_diff_attention(ctx.q_len, ctx.pos0, self.H // self.G, self.G, None, ops.SIGMOID_MMA_ROWS,
+                                   ops.SIGMOID_DECODE_ROWS, ops.SIGMOID_MAX_SPLITS,
+                                   int(ctx.options.get("attention_target_blocks", 296)), ctx.options.get("attention_splits"))
+        for k, v in plan.items():
+            ctx.inputs.add(name + k, np.asarray(v, np.int32))
+        ctx.memo[key] = dict(name=name, n_pre=len(plan["pre"]) // 2, n_dec=len(plan["dec"]) // 4,
+                             n_slots=len(plan["slots"]) // 2)
 
     def forward(self, ctx, h, run, out="delta"):
         ops, N = ctx.ops, ctx.N
@@ -91,9 +123,26 @@ class SigmoidAttention:
 
     def attend(self, ctx, q, o, table, kpool, vpool):
         ops = ctx.ops
+        H, G, dim, vdim = self.H, self.G, self.dim, self.vdim
         page, pages = ctx.cache.page_size, ctx.cache.pool_pages
-        ops.sigmoid_attention_simple(q, o, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, self.slopes,
-                                     self.pb, self.H, self.G, self.dim, self.vdim, page, pages, self.scale, ctx.err)
+        if not self.uses_mma(ctx):
+            ops.sigmoid_attention_simple(q, o, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, self.slopes,
+                                         self.pb, H, G, dim, vdim, page, pages, self.scale, ctx.err)
+            return
+        import torch
+        plan = ctx.memo[self.plan_key()]
+        nm = plan["name"]
+        seqs = (ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"))
+        tail = (table, kpool, vpool, self.slopes, self.pb, H, G, dim, vdim, page, pages, self.scale, ctx.err)
+        if plan["n_pre"]:
+            ops.sigmoid_attention_mma(q, o, ctx.dev(nm + "pre"), plan["n_pre"], *seqs, *tail)
+        if plan["n_dec"]:
+            part_o = None
+            if plan["n_slots"]:
+                n = plan["n_slots"] * G * ops.SIGMOID_MAX_SPLITS * ops.SIGMOID_DECODE_ROWS
+                part_o = ctx.ws.get("sigattn_part_o", n, (vdim,), torch.float32, reserve=0)
+            ops.sigmoid_attention_mma_decode(q, o, ctx.dev(nm + "dec"), plan["n_dec"], ctx.dev(nm + "slots"),
+                                             plan["n_slots"], part_o, *seqs, *tail)
 
 
 register("mixer", "sigmoid_attention", SigmoidAttention)

@@ -142,8 +142,9 @@ def routed(W, p, f, h):
     return out
 
 
-def forward(cfg, W, tokens, keep_layers=False):
-    """-> logits (T, vocab) float64 (and the stream every layer hands on, when asked)"""
+def forward(cfg, W, tokens, keep_layers=False, keep_results=False):
+    """-> logits (T, vocab) float64 (and the stream every layer hands on, when asked; keep_results: instead of it the
+    embedding's output and every layer's own result, before the depth average)"""
     W = {k: v.to(F64) if v.is_floating_point() else v for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     t = torch.as_tensor(tokens, dtype=torch.long)
@@ -164,4 +165,6 @@ def forward(cfg, W, tokens, keep_layers=False):
         x = sum(W[p + "dwa"][j] * history[j] for j in range(i + 2))
         handed.append(x)
     logits = dyt(W, "final.norm", x) @ W["head"].T
+    if keep_results:
+        return logits, torch.stack(history)
     return (logits, torch.stack(handed)) if keep_layers else logits
