@@ -697,6 +697,34 @@ def sufopel_configs(size, layers, vocab=32000, context=8192):
     return sf, ll
 
 
+# Layer sizes for `--design tosevik`: three retention layers to one layer of two mixers side by side (attention with
+# sigmoid weights beside retention), routed experts with a gated shared expert in every layer.  Heads of 128 x 128, a kv
+# head to four query heads.  The Sufopel decoder beside it -- the closest design the engine has: recurrent layers with a
+# matrix state per head, one attention layer in four, routed experts -- has the same width, layers, heads, head sizes and
+# experts.
+TOSEVIK_SIZES = {
+    "1b": dict(width=2048, heads=16, dim=128, ff=1408, experts=64, top=6, groups=8, keep=4, shared=2816),
+    "3b": dict(width=3072, heads=24, dim=128, ff=1536, experts=64, top=6, groups=8, keep=4, shared=3072),
+    "8b": dict(width=4096, heads=32, dim=128, ff=2048, experts=64, top=8, groups=8, keep=4, shared=4096),
+}
+
+
+def tosevik_configs(size, layers, vocab=32000, context=8192):
+    from mashbox_b200.config.tosevik import ExpertsFF, PairMixer, RetentionMixer, SigmoidMixer, TosevikConfig, TosevikLayer
+    z = TOSEVIK_SIZES[size]
+    D, H, dim = z["width"], z["heads"], z["dim"]
+    decay = tuple(1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H))
+    ret = RetentionMixer(heads=H, dim=dim, vdim=dim, decay=decay, rot_dims=dim, rot_base=10000.0)
+    sig = SigmoidMixer(heads=H, kv_heads=max(1, H // 4), dim=dim, vdim=dim, scale=dim ** -0.5, temp_coef=0.1, temp_every=1024)
+    moe = ExpertsFF(ff=z["ff"], experts=z["experts"], top=z["top"], scale=2.5, groups=z["groups"], keep=z["keep"],
+                    shared_ff=z["shared"])
+    tv = TosevikConfig("Tosevik", width=D, vocab=vocab, norm_eps=1e-6, layers=tuple(
+        TosevikLayer("parallel", PairMixer(sig, ret), moe) if i % 4 == 3 else TosevikLayer("retention", ret, moe)
+        for i in range(layers)))
+    sf = sufopel_configs(size, layers, vocab, context)[0]
+    return tv, sf
+
+
 def run_design(a):
     """`--design luzosun --size 1b|3b|8b`: prefill and decode throughput of the Luzosun decoder and of the Llama decoder
     of equal size through the step function (random bf16 weights, `--layers` layers, default 4), and the kernels that
@@ -711,7 +739,12 @@ def run_design(a):
     dev = "cuda:0"
     layers = a.layers or 4
     design = a.design
-    if design == "sufopel":
+    other = "llama"
+    if design == "tosevik":
+        z, other = TOSEVIK_SIZES[a.size], "sufopel"
+        cfgs = dict(zip((design, other), tosevik_configs(a.size, layers, context=a.context)))
+        single_kernels = tosevik_kernels
+    elif design == "sufopel":
         z = SUFOPEL_SIZES[a.size]
         cfgs = dict(zip((design, "llama"), sufopel_configs(a.size, layers, context=a.context)))
         single_kernels = sufopel_kernels
@@ -783,7 +816,7 @@ def run_design(a):
         del eng, runner, cache
         torch.cuda.empty_cache()
     out["kernels"] = single_kernels(a, z, P, B, ctx, pk)
-    out[f"ratio_{design}_to_llama"] = {k: out[design][k] / out["llama"][k] for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    out[f"ratio_{design}_to_{other}"] = {k: out[design][k] / out[other][k] for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
     print(json.dumps({"impl": "ours", "design": design, "size": a.size, "layers": layers, "prefill_tokens": P, "batch": B,
                       "context": ctx, "dtype": "bf16", "data": "synthetic", "peaks": pk, "clocks": clocks.stop(), **out}))
     return 0
@@ -899,6 +932,155 @@ def sufopel_kernels(a, z, P, B, ctx, pk):
         res[f"post_norm_add_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
         us = timed(lambda: ops.add_rmsnorm(x, delta, None, w, 1e-6, nrm))
         res[f"add_norm_llama_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+    return res
+
+
+def tosevik_kernels(a, z, P, B, ctx, pk):
+    """The kernels of the Tosevik decoder, each beside the Sufopel decoder's kernel of the like job at equal sizes (the
+    recurrence beside the delta rule, attention with sigmoid weights beside latent attention and beside softmax attention
+    over as many kv heads, the stream's kernels beside the post norm): CUDA-event time of single launches after an L2
+    flush, and the fraction of the measured peak (copy bandwidth for the memory-bound ones, bf16 tensor throughput for
+    the products) that the algorithmic bytes or FLOPs come to."""
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.parts.attention import PagedAttention
+    from mashbox_b200.parts.sigmoid_attention import SigmoidAttention, geometric_slopes
+    dev = "cuda:0"
+    D, H, dim, F, E, top, page = z["width"], z["heads"], z["dim"], z["ff"], z["experts"], z["top"], 16
+    G = max(1, H // 4)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    bf = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    f32 = lambda *s: torch.randn(*s, generator=gen, device=dev) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = ops.new_error_word(dev)
+
+    def timed(f):
+        for _ in range(3):
+            f()
+        ts = []
+        for _ in range(max(5, a.steps // 4)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    mem = lambda us, nbytes: {"us": us, "gbs": nbytes / us / 1e3, "frac_of_copy_peak": nbytes / us / 1e3 / pk["hbm_gbs"]}
+    mat = lambda us, flops: {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / pk["bf16_tflops"]}
+    res = {}
+    # ---- the two recurrences: a prompt of P tokens; B sequences of one token (state in, state out)
+    decay = torch.tensor([1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)], device=dev)
+    for form, N, S in (("prompt", P, 1), ("decode", B, B)):
+        q, k, v, o = f32(N, H * dim), f32(N, H * dim) * dim ** -0.5, f32(N, H * dim), f32(N, H * dim)
+        state = torch.zeros(S, H * dim * dim, device=dev)
+        seq = (i32([i * (N // S) for i in range(S)]), i32([N // S] * S), i32(list(range(S))))
+        nbytes = 2 * S * H * dim * dim * 4 + N * H * dim * 4 * 4
+        for name, chunked in (("retention", form == "prompt"), ("retention_scan", False)):
+            us = timed(lambda: ops.retention(q, k, v, decay, o, state, seq, H, dim, dim, chunked=chunked))
+            r = mem(us, nbytes)
+            r["gflops_fp32"] = N * H * dim * dim * 4 / us / 1e3                  # decay + write, read: 4 per element and token
+            res[f"{name}_{form}"] = r
+            state.zero_()
+        g, beta = torch.rand(N, H * dim, generator=gen, device=dev), torch.rand(N, H, generator=gen, device=dev)
+        us = timed(lambda: ops.delta_rule(q, k, v, g, beta, o, state, seq, H, H, dim, dim))
+        res[f"delta_rule_sufopel_{form}"] = mem(us, nbytes + N * H * dim * 4)
+        # what stands around the recurrence: rotation and widening of q, k, v; the unit-rms heads times the gate
+        rows, freqs = bf(N, 4 * H * dim), torch.rand(dim // 2, generator=gen, device=dev)
+        pos = torch.arange(N, dtype=torch.int32, device=dev)
+        us = timed(lambda: ops.retention_prep(rows, 0, H * dim, 2 * H * dim, pos, freqs, q, k, v, H, dim, dim, dim, dim ** -0.5))
+        res[f"retention_prep_{form}"] = mem(us, N * H * dim * 3 * (2 + 4))
+        gated = torch.empty(N, H * dim, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.gated_rms(o, rows[:, 3 * H * dim:], None, gated, H, dim, 1e-6, silu=True))
+        res[f"retention_gated_norm_{form}"] = mem(us, N * H * dim * (4 + 2 + 2))
+    # ---- attention: sigmoid weights (H heads on G kv heads); beside it softmax attention of the same heads, and Sufopel's
+    #      latent attention (one shared row of `dim` values per position)
+    sig = SigmoidAttention(D, H, G, dim, dim, dim ** -0.5, 1e-6, slopes=geometric_slopes(H, 8.0), q_temp=(0.1, 1024))
+    sig.slopes, sig.pb = torch.tensor(sig.slope_values, device=dev), f32(H)
+    att = PagedAttention(H, G, dim)
+    lat = PagedAttention(H, 1, dim, None, dim ** -0.5)
+    for name, core, KV in (("sigmoid_attention", sig, G), ("attention_softmax", att, G), ("latent_attention_sufopel", lat, 1)):
+        for form, N, S, klen in (("prompt", P, 1, P), ("decode", B, B, ctx)):
+            pages = S * -(-klen // page)
+            table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(S, -1)
+            kp, vp = bf(pages, KV, page, dim), bf(pages, KV, page, dim)
+            if core is lat:
+                vp = kp
+            q, o = bf(N, H * dim), torch.empty(N, H * dim, device=dev, dtype=torch.bfloat16)
+            q_len = [N // S] * S
+            ctx_ = _PlanContext(ops, dev, q_len, [klen - n for n in q_len], page, pages, err)
+            core.prepare(ctx_)
+            ctx_.inputs.upload()
+            if core is sig:
+                us = timed(lambda: core.attend(ctx_, q, o, table, kp, vp))
+            else:
+                us = timed(lambda: core.attend(ctx_, q, H * dim, o, table, kp, vp))
+            nbytes = (1 if core is lat else 2) * S * klen * KV * dim * 2 + 2 * N * H * dim * 2
+            if form == "prompt":
+                res[f"{name}_prompt"] = mat(us, 4 * H * dim * P * P / 2)
+                if core is sig:             # a weight goes into the second product as two bf16 numbers: 3 products, not 2
+                    res[f"{name}_prompt"]["tflops_issued"] = 6 * H * dim * P * P / 2 / us / 1e6
+            else:
+                res[f"{name}_decode"] = mem(us, nbytes)
+        if core is sig:                      # the kernel in front of it: norms over whole rows, temperature, cache write
+            for form, N in (("prompt", P), ("decode", B)):
+                rows, qn = bf(N, (H + 2 * G) * dim), torch.empty(N, H * dim, device=dev, dtype=torch.bfloat16)
+                pages = -(-N // page)
+                table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, -1)
+                kp, vp = bf(pages, G, page, dim), bf(pages, G, page, dim)
+                pos, row = torch.arange(N, dtype=torch.int32, device=dev), torch.zeros(N, dtype=torch.int32, device=dev)
+                qw, kw = f32(H * dim), f32(G * dim)
+                us = timed(lambda: ops.sigmoid_attention_prep(rows, qw, kw, pos, row, table, qn, kp, vp, H, G, dim, dim, page,
+                                                               pages, 1e-6, 0.1, 1024, err))
+                res[f"sigmoid_attention_prep_{form}"] = mem(us, 2 * N * (H + 2 * G) * dim * 2)
+    # ---- the experts: the same kernels as Sufopel's with another activation and, in the last one, the gated shared expert
+    wg, wu, wd = bf(E, F, D), bf(E, F, D), bf(E, D, F)
+    for form, N in (("prompt", P), ("decode", B)):
+        h = bf(N, D)
+        ids = torch.stack([torch.randperm(E, generator=gen, device=dev)[:top] for _ in range(N)]).int().contiguous()
+        wts, shared, gate = torch.rand(N, top, generator=gen, device=dev), bf(N, D), f32(N, 1)
+        touched = len(set(ids.flatten().tolist()))
+        for name, lim, alpha, shift, extra in (("experts", float("inf"), 1.0, 0.0, (shared, gate)), ("experts_sufopel", 7.0, 1.702, 1.0, (None, None))):
+            if form == "prompt":
+                T = ops.moe_tc5_tiles(N, top, E)
+                out = torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+                rows, act2 = torch.empty(128 * T, D, device=dev, dtype=torch.bfloat16), torch.empty(128 * T, F, device=dev, dtype=torch.bfloat16)
+                y2, places = torch.empty(128 * T, D, device=dev), torch.empty(N * top + T, dtype=torch.int32, device=dev)
+                wgu2 = torch.cat([wg, wu], 1).contiguous()
+                us = timed(lambda: ops.moe_tc5(h, ids, wts, wgu2, wd, out, rows, act2, y2, places, lim, alpha, shift, *extra))
+                res[f"{name}_prompt"] = mat(us, 2 * N * top * 3 * F * D)
+                need = max(2 * N * top * 3 * F * D / (pk["bf16_tflops"] * 1e6), touched * 3 * F * D * 2 / (pk["hbm_gbs"] * 1e3))
+                res[f"{name}_prompt"].update(frac_of_roofline=need / us)
+                del wgu2, rows, act2, y2
+            else:
+                y, out = torch.empty(N, top, D, device=dev), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+                us = timed(lambda: (ops.moe_experts(h, ids, wg, wu, wd, y, lim, alpha, None, shift), ops.moe_combine(y, wts, out, *extra)))
+                res[f"{name}_decode"] = mem(us, touched * 3 * F * D * 2)
+                res[f"{name}_decode"]["experts_touched"] = touched
+        z_ = f32(N, E + 1)
+        idc, wtc = torch.empty(N, top, dtype=torch.int32, device=dev), torch.empty(N, top, device=dev)
+        us = timed(lambda: ops.moe_select(z_, None, idc, wtc, z["groups"], z["keep"], experts=E, softmax=True, worth="max", scale=2.5))
+        res[f"choice_softmax_{form}"] = {"us": us}
+        corr = f32(E)
+        us = timed(lambda: ops.moe_select(z_, corr, idc, wtc, z["groups"], z["keep"], experts=E))
+        res[f"choice_sufopel_{form}"] = {"us": us}
+    # ---- the stream: add + Dynamic Tanh; add + depth average + next norm; two normed outputs halved; Sufopel's post norm
+    L = 4
+    for form, N in (("prompt", P), ("decode", B)):
+        x, delta, delta2, w, b = f32(N, D), bf(N, D), bf(N, D), f32(D), f32(D)
+        nrm = torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.dyt(x, delta, 0.5, w, b, nrm))
+        res[f"add_dyt_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+        hist, coef = torch.zeros(L + 1, N, D, device=dev), f32(L + 1)
+        us = timed(lambda: ops.depth_average(x, delta, hist, coef, L - 1, normed=nrm, next_norm=(0.5, w, b)))
+        res[f"depth_average_{form}"] = mem(us, N * D * (4 + 2 + 4 + 4 * L + 4 + 2))       # the last layer's: L earlier results read
+        us = timed(lambda: ops.rms_pair_mean(delta, delta2, w, b, nrm, 1e-6))
+        res[f"pair_mean_{form}"] = mem(us, N * D * 3 * 2)
+        us = timed(lambda: ops.post_norm_add(x, delta, w, 1e-6, w, 1e-6, nrm))
+        res[f"post_norm_add_sufopel_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
     return res
 
 
@@ -1095,8 +1277,9 @@ def main():
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
     ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--design", default="", choices=("", "luzosun", "sufopel"),
-                    help="another design beside the Llama decoder of equal size (prefill, decode, single kernels)")
+    ap.add_argument("--design", default="", choices=("", "luzosun", "sufopel", "tosevik"),
+                    help="another design beside the Llama decoder of equal size (tosevik: beside the Sufopel decoder): "
+                    "prefill, decode, single kernels")
     ap.add_argument("--size", default="8b", choices=tuple(DESIGN_SIZES), help="--design: the layer sizes")
     ap.add_argument("--workload-warm", type=int, default=1, help="workloads: run the workload once untimed first")
     a = ap.parse_args()
