@@ -13,15 +13,17 @@
 //                    and k turn by position * freq_i (dim i with dim i + R/2), k times a constant after that; q, k, v
 //                    left in float32
 //   retention_scan   the recurrence, token by token (decode steps, short portions, the whole float32 path)
-//   retention_chunk  the same recurrence for long stretches, a chunk of RC_T tokens at a time: inside a chunk
-//                    o_t = decay^(t+1) S0^T q_t + sum_(s <= t) decay^(t-s) (q_t . k_s) v_s, and
-//                    S <- decay^n S0 + sum_s decay^(n-1-s) k_s v_s^T, all in float32; the tokens of a chunk run side by
-//                    side instead of one after the other
+//   the split form   the same recurrence for long stretches.  The decay is a constant of the head, so a sequence can be
+//                    cut into segments that run side by side: every segment is scanned from a zero state (the first one
+//                    from the sequence's own), which gives the part of every o that the segment's own tokens make and
+//                    the state E_j the segment adds; a small kernel chains S0_(j+1) = decay^n S0_j + E_j; a second pass
+//                    adds decay^(t+1) S0_j^T q_t to the t-th token of segment j.  All of it in float32.
 #include "common.cuh"
 
 #define RT_THREADS 128
 #define RT_LANES 8
-#define RT_BATCH 16
+#define RT_BATCH 8
+#define RT_STAGES 4
 
 // grid (N, H).  rows (N, stride) holds q at q_off, k at k_off (H dim each), v at v_off (H vdim).
 template <typename T>
@@ -54,162 +56,244 @@ __global__ void retention_prep_kernel(const T* __restrict__ rows, int stride, in
     for (int c = threadIdx.x; c < vdim; c += blockDim.x) v[((size_t)n * H + h) * vdim + c] = mb_load(vs + c);
 }
 
-// grid (column tiles, H, sequences), RT_THREADS threads: RT_THREADS / RT_LANES columns a block.  A thread holds R
-// values of its column: channels r * RT_LANES + lane, so that the lanes of a column read one contiguous stretch of a
-// token's q and k from shared memory and the columns of a warp read the same one.  dim <= R * RT_LANES.
-template <int R>
+// two floats in one 64-bit register pair, and the fused multiply-add on such pairs (one issue slot, two results, each
+// rounded as the single one is)
+__device__ __forceinline__ uint64_t rt_pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void rt_unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t rt_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// global to shared memory without a register in between; size 0: the destination is set to zero
+__device__ __forceinline__ void rt_cp16(float* smem, const float* gmem, int size) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
+}
+__device__ __forceinline__ void rt_cp4(float* smem, const float* gmem, int size) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
+}
+
+// The stretch of tokens a block walks.  Whole sequences: block z is sequence z.  Segments: a sequence of n tokens is cut
+// into ceil(n / seg) segments, numbered through all sequences in order; block z finds its own by walking the lengths
+// (there are few sequences in a step).  Returns false for a block beyond the last segment.
+struct RtStretch {
+    int s, j, first, len, z0;       // sequence, segment within it, first token, tokens, number of the sequence's segment 0
+};
+__device__ __forceinline__ bool rt_find(int z, int S, int seg, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                        RtStretch& r) {
+    int base = 0;
+    for (int s = 0; s < S; s++) {
+        const int n = q_len[s], ns = (n + seg - 1) / seg;
+        if (z < base + ns) {
+            r.s = s; r.j = z - base; r.z0 = base;
+            r.first = q_start[s] + r.j * seg;
+            r.len = min(seg, n - r.j * seg);
+            return true;
+        }
+        base += ns;
+    }
+    return false;
+}
+
+// grid (column tiles, H, sequences or segments), RT_THREADS threads: RT_THREADS / RT_LANES columns a block.  A thread
+// holds 4 R4 values of its column, channels r4 * 4 RT_LANES + 4 lane + (0..3): the lanes of a column read one contiguous
+// stretch of a token's q and k from shared memory, 16 bytes each, and the columns of a warp read the same one.
+// dim <= 4 R4 RT_LANES.  The tokens' q, k, v come through a ring of RT_STAGES stages of RT_BATCH tokens, copied
+// asynchronously: DRAM is a microsecond away and a stage is worked through in a fraction of that.
+//   MODE 0  whole sequences: the state comes from the sequence's slot and goes back there
+//   MODE 1  segments: segment 0 starts from the slot, the others from zero; the state a segment ends with goes to
+//           carry[z]; o holds what the segment's own tokens (and for segment 0 the slot's state) give
+//   MODE 2  the rest of o for the segments after the first: carry[z] now holds the state S0 the segment starts from,
+//           and o_t += decay^(t+1) S0^T q_t for its t-th token; nothing is written but o
+template <int R4, int MODE>
 __global__ void __launch_bounds__(RT_THREADS)
 retention_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                       const float* __restrict__ decay, float* __restrict__ o, float* __restrict__ state,
-                      long long state_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                      const int* __restrict__ state_slot, int H, int dim, int vdim) {
-    constexpr int DP = R * RT_LANES, COLS = RT_THREADS / RT_LANES, BT = RT_BATCH;
-    __shared__ __align__(16) float sq[BT][DP];
-    __shared__ __align__(16) float sk[BT][DP];
-    __shared__ float sv[BT][COLS];
-    const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * COLS;
+                      long long state_stride, int state_vec, float* __restrict__ carry, const int* __restrict__ q_start,
+                      const int* __restrict__ q_len, const int* __restrict__ state_slot, int S, int seg, int H, int dim,
+                      int vdim) {
+    constexpr int DP = 4 * R4 * RT_LANES, COLS = RT_THREADS / RT_LANES, BT = RT_BATCH;
+    extern __shared__ __align__(16) float ring[];
+    typedef float (*RowsDP)[BT][DP];
+    typedef float (*RowsC)[BT][COLS];
+    RowsDP sq = reinterpret_cast<RowsDP>(ring), sk = sq + RT_STAGES;
+    RowsC sv = reinterpret_cast<RowsC>(ring + 2 * RT_STAGES * BT * DP);
+    const int h = blockIdx.y, col0 = blockIdx.x * COLS;
     const int lane = threadIdx.x & (RT_LANES - 1), cg = threadIdx.x / RT_LANES, col = col0 + cg;
-    const int a = q_start[s], len = q_len[s];
+    RtStretch w;
+    if (MODE == 0) {
+        w.s = blockIdx.z; w.j = 0; w.z0 = 0; w.first = q_start[w.s]; w.len = q_len[w.s];
+    } else {
+        if (!rt_find(blockIdx.z, S, seg, q_start, q_len, w)) return;
+        if (MODE == 2 && w.j == 0) return;
+    }
+    const int a = w.first, len = w.len;
     const float dec = decay[h];
     const bool in = col < vdim;
-    float* S = state + (size_t)state_slot[s] * state_stride + ((size_t)h * vdim + (in ? col : 0)) * dim;
-    float st[R];
+    const size_t head_off = ((size_t)h * vdim + (in ? col : 0)) * dim;
+    float* slot = state + (size_t)state_slot[w.s] * state_stride + head_off;
+    float* mine = MODE == 0 ? slot : carry + (size_t)blockIdx.z * H * vdim * dim + head_off;
+    const float* src = MODE == 2 ? mine : ((MODE == 0 || w.j == 0) ? slot : nullptr);
+    const bool src_vec = (dim & 3) == 0 && (MODE == 2 || state_vec);
+    float* dst = MODE == 2 ? nullptr : mine;
+    const bool dst_vec = (dim & 3) == 0 && (MODE == 1 || state_vec);
+    uint64_t st[2 * R4];            // the column in pairs: channels (i, i + 1)
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int i = r * RT_LANES + lane;
-        st[r] = (in && i < dim) ? S[i] : 0.0f;
+    for (int r4 = 0; r4 < R4; r4++) {
+        const int i = r4 * 4 * RT_LANES + lane * 4;
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (src && in) {
+            if (src_vec) {
+                if (i < dim) x = *reinterpret_cast<const float4*>(src + i);
+            } else {
+                if (i < dim) x.x = src[i];
+                if (i + 1 < dim) x.y = src[i + 1];
+                if (i + 2 < dim) x.z = src[i + 2];
+                if (i + 3 < dim) x.w = src[i + 3];
+            }
+        }
+        st[2 * r4] = rt_pack2(x.x, x.y);
+        st[2 * r4 + 1] = rt_pack2(x.z, x.w);
     }
-    for (int t0 = 0; t0 < len; t0 += BT) {
+    // 16 bytes a copy where every row starts on a 16-byte boundary (dim and vdim multiples of 4), else 4
+    const bool vec = (dim & 3) == 0 && (vdim & 3) == 0;
+    auto fetch = [&](int buf, int t0) {
         const int nb = min(BT, len - t0);
-        for (int idx = threadIdx.x; idx < nb * DP; idx += RT_THREADS) {
-            const int tt = idx / DP, i = idx - tt * DP;
-            const size_t n = (size_t)(a + t0 + tt);
-            sq[tt][i] = i < dim ? q[(n * H + h) * dim + i] : 0.0f;
-            sk[tt][i] = i < dim ? k[(n * H + h) * dim + i] : 0.0f;
+        if (vec) {
+            for (int idx = threadIdx.x; idx < nb * (DP / 4); idx += RT_THREADS) {
+                const int tt = idx / (DP / 4), i = (idx - tt * (DP / 4)) * 4;
+                const size_t n = (size_t)(a + t0 + tt);
+                const int sz = i < dim ? 16 : 0, ii = i < dim ? i : 0;
+                rt_cp16(&sq[buf][tt][i], q + (n * H + h) * dim + ii, sz);
+                if (MODE != 2) rt_cp16(&sk[buf][tt][i], k + (n * H + h) * dim + ii, sz);
+            }
+            if (MODE != 2)
+                for (int idx = threadIdx.x; idx < nb * (COLS / 4); idx += RT_THREADS) {
+                    const int tt = idx / (COLS / 4), c = (idx - tt * (COLS / 4)) * 4;
+                    const bool ok = col0 + c < vdim;
+                    rt_cp16(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (ok ? col0 + c : 0), ok ? 16 : 0);
+                }
+        } else {
+            for (int idx = threadIdx.x; idx < nb * DP; idx += RT_THREADS) {
+                const int tt = idx / DP, i = idx - tt * DP;
+                const size_t n = (size_t)(a + t0 + tt);
+                const int sz = i < dim ? 4 : 0, ii = i < dim ? i : 0;
+                rt_cp4(&sq[buf][tt][i], q + (n * H + h) * dim + ii, sz);
+                if (MODE != 2) rt_cp4(&sk[buf][tt][i], k + (n * H + h) * dim + ii, sz);
+            }
+            if (MODE != 2)
+                for (int idx = threadIdx.x; idx < nb * COLS; idx += RT_THREADS) {
+                    const int tt = idx / COLS, c = idx - tt * COLS;
+                    const bool ok = col0 + c < vdim;
+                    rt_cp4(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (ok ? col0 + c : 0), ok ? 4 : 0);
+                }
         }
-        for (int idx = threadIdx.x; idx < nb * COLS; idx += RT_THREADS) {
-            const int tt = idx / COLS, c = idx - tt * COLS;
-            sv[tt][c] = col0 + c < vdim ? v[((size_t)(a + t0 + tt) * H + h) * vdim + col0 + c] : 0.0f;
-        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    // every iteration commits one group (an empty one beyond the end), so the group of the stage that is worked on next
+    // is always the (RT_STAGES - 1)-th from the newest
+    for (int p = 0; p < RT_STAGES - 1; p++) {
+        if (p * BT < len) fetch(p, p * BT);
+        else asm volatile("cp.async.commit_group;\n" ::);
+    }
+    const uint64_t zero2 = rt_pack2(0.0f, 0.0f), dec2 = rt_pack2(dec, dec);
+    for (int t0 = 0, it = 0; t0 < len; t0 += BT, it++) {
+        const int nb = min(BT, len - t0), buf = it % RT_STAGES;
+        const int ahead = t0 + (RT_STAGES - 1) * BT;
+        if (ahead < len) fetch((it + RT_STAGES - 1) % RT_STAGES, ahead);       // the stage worked on last iteration is free
+        else asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(RT_STAGES - 1));
         __syncthreads();
+        float pw = MODE == 2 ? powf(dec, (float)(t0 + 1)) : 0.0f;              // decay^(t + 1) at the stage's first token
+#pragma unroll 2
         for (int tt = 0; tt < nb; tt++) {
-            const float vv = sv[tt][cg];
-            float acc0 = 0.0f, acc1 = 0.0f;
+            uint64_t asum0 = zero2, asum1 = zero2;
+            if (MODE != 2) {
+                const float vv = sv[buf][tt][cg];
+                const uint64_t v2 = rt_pack2(vv, vv);
 #pragma unroll
-            for (int r = 0; r < R; r += 2) {
-                st[r] = fmaf(sk[tt][r * RT_LANES + lane], vv, dec * st[r]);
-                acc0 = fmaf(st[r], sq[tt][r * RT_LANES + lane], acc0);
-                if (r + 1 < R) {
-                    st[r + 1] = fmaf(sk[tt][(r + 1) * RT_LANES + lane], vv, dec * st[r + 1]);
-                    acc1 = fmaf(st[r + 1], sq[tt][(r + 1) * RT_LANES + lane], acc1);
+                for (int r4 = 0; r4 < R4; r4++) {
+                    const float4 kk = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * RT_LANES + lane * 4]);
+                    const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * RT_LANES + lane * 4]);
+                    // the decayed value is a product rounded once; the new key and value are added by one fused step
+                    st[2 * r4] = rt_fma2(rt_pack2(kk.x, kk.y), v2, rt_fma2(st[2 * r4], dec2, zero2));
+                    st[2 * r4 + 1] = rt_fma2(rt_pack2(kk.z, kk.w), v2, rt_fma2(st[2 * r4 + 1], dec2, zero2));
+                    asum0 = rt_fma2(st[2 * r4], rt_pack2(qq.x, qq.y), asum0);
+                    asum1 = rt_fma2(st[2 * r4 + 1], rt_pack2(qq.z, qq.w), asum1);
+                }
+            } else {
+#pragma unroll
+                for (int r4 = 0; r4 < R4; r4++) {
+                    const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * RT_LANES + lane * 4]);
+                    asum0 = rt_fma2(st[2 * r4], rt_pack2(qq.x, qq.y), asum0);
+                    asum1 = rt_fma2(st[2 * r4 + 1], rt_pack2(qq.z, qq.w), asum1);
                 }
             }
-            float acc = acc0 + acc1;
+            float a0, a1, a2, a3;
+            rt_unpack2(asum0, a0, a1);
+            rt_unpack2(asum1, a2, a3);
+            float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
             for (int m = 1; m < RT_LANES; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-            if (lane == 0 && in) o[((size_t)(a + t0 + tt) * H + h) * vdim + col] = acc;
+            if (lane == 0 && in) {
+                float* dsto = o + ((size_t)(a + t0 + tt) * H + h) * vdim + col;
+                if (MODE == 2) *dsto = fmaf(pw, acc, *dsto);
+                else *dsto = acc;
+            }
+            if (MODE == 2) pw *= dec;
         }
         __syncthreads();
     }
+    if (dst && in) {
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int i = r * RT_LANES + lane;
-        if (in && i < dim) S[i] = st[r];
+        for (int r4 = 0; r4 < R4; r4++) {
+            const int i = r4 * 4 * RT_LANES + lane * 4;
+            float4 x;
+            rt_unpack2(st[2 * r4], x.x, x.y);
+            rt_unpack2(st[2 * r4 + 1], x.z, x.w);
+            if (dst_vec) {
+                if (i < dim) *reinterpret_cast<float4*>(dst + i) = x;
+            } else {
+                if (i < dim) dst[i] = x.x;
+                if (i + 1 < dim) dst[i + 1] = x.y;
+                if (i + 2 < dim) dst[i + 2] = x.z;
+                if (i + 3 < dim) dst[i + 3] = x.w;
+            }
+        }
     }
 }
 
-// ---------------------------------------------------------------------------------------------------------------------
-// The chunk form.  grid (column tiles of RC_COLS, H, sequences), RC_THREADS threads.  A block keeps its RC_COLS columns
-// of the state in shared memory (dim x RC_COLS) and walks the sequence in chunks of RC_T tokens:
-//   A[t][s] = decay^(t-s) (q_t . k_s) for s <= t      (RC_T x RC_T, every block of the head computes it: dim FMAs each)
-//   o[t][c] = decay^(t+1) sum_i q_t[i] S[i][c] + sum_(s <= t) A[t][s] v_s[c]
-//   S[i][c] = decay^n S[i][c] + sum_s decay^(n-1-s) k_s[i] v_s[c]
-// Powers of the decay come from a table made once per block (decay^0 .. decay^RC_T, by repeated multiplication).
-#define RC_T 32
-#define RC_COLS 32
-#define RC_THREADS 256
-#define RC_MAX_DIM 256
-
-__global__ void __launch_bounds__(RC_THREADS)
-retention_chunk_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                       const float* __restrict__ decay, float* __restrict__ o, float* __restrict__ state,
-                       long long state_stride, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                       const int* __restrict__ state_slot, int H, int dim, int vdim) {
-    extern __shared__ __align__(16) float sm[];
-    const int DPAD = dim + 1;                       // rows of q and k one float longer: t-major reads hit different banks
-    float* sS = sm;                                 // [dim][RC_COLS]
-    float* sq = sS + (size_t)dim * RC_COLS;         // [RC_T][DPAD]
-    float* sk = sq + RC_T * DPAD;                   // [RC_T][DPAD]
-    float* sv = sk + RC_T * DPAD;                   // [RC_T][RC_COLS]
-    float* sA = sv + RC_T * RC_COLS;                // [RC_T][RC_T + 1]
-    float* pw = sA + RC_T * (RC_T + 1);             // [RC_T + 1]
-    const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * RC_COLS, tid = threadIdx.x;
-    const int a = q_start[s], len = q_len[s];
-    const float dec = decay[h];
-    float* S = state + (size_t)state_slot[s] * state_stride + (size_t)h * vdim * dim;
-    if (tid == 0) {
-        float p = 1.0f;
-        for (int i = 0; i <= RC_T; i++) { pw[i] = p; p *= dec; }
+// Between the two passes over the segments: carry[z] comes in as the state segment z ends with when it starts from
+// zero (segment 0: from the slot's state), E_j, and leaves as the state segment z starts from,
+//     S0_0 = 0,   S0_(j+1) = decay^(n_j) S0_j + E_j        (n_j tokens in segment j)
+// and what the last segment ends with goes to the sequence's slot.  grid (blocks over H vdim dim, sequences): a thread
+// owns one value of the state and walks the sequence's segments in order.
+__global__ void retention_carry_kernel(float* __restrict__ carry, const float* __restrict__ decay, float* __restrict__ state,
+                                       long long state_stride, const int* __restrict__ q_len,
+                                       const int* __restrict__ state_slot, int seg, int H, int dim, int vdim) {
+    const int s = blockIdx.y;
+    const size_t per = (size_t)H * vdim * dim, e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    int z0 = 0;
+    for (int i = 0; i < s; i++) z0 += (q_len[i] + seg - 1) / seg;
+    const int n = q_len[s], ns = (n + seg - 1) / seg;
+    if (ns == 0) return;
+    const float dec = decay[e / ((size_t)vdim * dim)], whole = powf(dec, (float)seg);
+    float cur = 0.0f;
+    for (int j = 0; j < ns; j++) {
+        float* p = carry + (size_t)(z0 + j) * per + e;
+        const float end = *p;
+        *p = cur;
+        const int nj = min(seg, n - j * seg);
+        cur = fmaf(nj == seg ? whole : powf(dec, (float)nj), cur, end);
     }
-    for (int idx = tid; idx < dim * RC_COLS; idx += RC_THREADS) {
-        const int c = idx / dim, i = idx - c * dim;             // the stored state is (vdim, dim): i runs fastest
-        sS[i * RC_COLS + c] = col0 + c < vdim ? S[(size_t)(col0 + c) * dim + i] : 0.0f;
-    }
-    __syncthreads();
-    for (int t0 = 0; t0 < len; t0 += RC_T) {
-        const int nb = min(RC_T, len - t0);
-        for (int idx = tid; idx < RC_T * dim; idx += RC_THREADS) {
-            const int tt = idx / dim, i = idx - tt * dim;
-            const size_t n = (size_t)(a + t0 + tt);
-            const bool ok = tt < nb;
-            sq[tt * DPAD + i] = ok ? q[(n * H + h) * dim + i] : 0.0f;
-            sk[tt * DPAD + i] = ok ? k[(n * H + h) * dim + i] : 0.0f;
-        }
-        for (int idx = tid; idx < RC_T * RC_COLS; idx += RC_THREADS) {
-            const int tt = idx / RC_COLS, c = idx - tt * RC_COLS;
-            sv[idx] = (tt < nb && col0 + c < vdim) ? v[((size_t)(a + t0 + tt) * H + h) * vdim + col0 + c] : 0.0f;
-        }
-        __syncthreads();
-        // A: RC_T * RC_T entries over RC_THREADS threads
-        for (int idx = tid; idx < RC_T * RC_T; idx += RC_THREADS) {
-            const int t = idx / RC_T, u = idx - t * RC_T;
-            float acc = 0.0f;
-            if (u <= t && t < nb) {
-                const float* qr = sq + t * DPAD;
-                const float* kr = sk + u * DPAD;
-                for (int i = 0; i < dim; i++) acc = fmaf(qr[i], kr[i], acc);
-                acc *= pw[t - u];
-            }
-            sA[t * (RC_T + 1) + u] = acc;
-        }
-        __syncthreads();
-        // o: RC_T * RC_COLS outputs; thread -> (t, c) with c fastest (the state's and v's reads run along banks)
-        for (int idx = tid; idx < RC_T * RC_COLS; idx += RC_THREADS) {
-            const int t = idx / RC_COLS, c = idx - t * RC_COLS;
-            if (t >= nb) continue;
-            float carried = 0.0f;
-            const float* qr = sq + t * DPAD;
-            for (int i = 0; i < dim; i++) carried = fmaf(qr[i], sS[i * RC_COLS + c], carried);
-            float acc = carried * pw[t + 1];
-            const float* ar = sA + t * (RC_T + 1);
-            for (int u = 0; u <= t; u++) acc = fmaf(ar[u], sv[u * RC_COLS + c], acc);
-            if (col0 + c < vdim) o[((size_t)(a + t0 + t) * H + h) * vdim + col0 + c] = acc;
-        }
-        __syncthreads();
-        // the state moves on by the chunk's nb tokens
-        const float all = pw[nb];
-        for (int idx = tid; idx < dim * RC_COLS; idx += RC_THREADS) {
-            const int i = idx / RC_COLS, c = idx - i * RC_COLS;
-            float acc = sS[idx] * all;
-            for (int u = 0; u < nb; u++) acc = fmaf(sk[u * DPAD + i] * pw[nb - 1 - u], sv[u * RC_COLS + c], acc);
-            sS[idx] = acc;
-        }
-        __syncthreads();
-    }
-    for (int idx = tid; idx < dim * RC_COLS; idx += RC_THREADS) {
-        const int c = idx / dim, i = idx - c * dim;
-        if (col0 + c < vdim) S[(size_t)(col0 + c) * dim + i] = sS[i * RC_COLS + c];
-    }
+    state[(size_t)state_slot[s] * state_stride + e] = cur;
 }
 
 template <typename T>
@@ -239,6 +323,35 @@ MB_API int mb_retention_prep_bf16(const void* rows, int stride, int q_off, int k
                                        vdim, R, k_scale, st);
 }
 
+static size_t rt_smem(int R4) {
+    return (size_t)RT_STAGES * RT_BATCH * (2 * 4 * R4 * RT_LANES + RT_THREADS / RT_LANES) * sizeof(float);
+}
+
+template <int R4, int MODE>
+static int rt_launch(dim3 grid, const float* q, const float* k, const float* v, const float* decay, float* o, float* state,
+                     long long state_stride, float* carry, const int* q_start, const int* q_len, const int* state_slot,
+                     int S, int seg, int H, int dim, int vdim, cudaStream_t st) {
+    const size_t smem = rt_smem(R4);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(retention_scan_kernel<R4, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    // 16-byte reads and writes of a slot's state need every column to start on such a boundary
+    const int state_vec = ((uintptr_t)state & 15) == 0 && (state_stride & 3) == 0 && (dim & 3) == 0;
+    retention_scan_kernel<R4, MODE><<<grid, RT_THREADS, smem, st>>>(q, k, v, decay, o, state, state_stride, state_vec, carry,
+                                                                    q_start, q_len, state_slot, S, seg, H, dim, vdim);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+#define RT_DISPATCH(MODE, ...)                                           \
+    (dim <= 32 ? rt_launch<1, MODE>(__VA_ARGS__)                         \
+     : dim <= 64 ? rt_launch<2, MODE>(__VA_ARGS__)                       \
+     : dim <= 128 ? rt_launch<4, MODE>(__VA_ARGS__) : rt_launch<8, MODE>(__VA_ARGS__))
+
 MB_API int mb_retention_scan(const float* q, const float* k, const float* v, const float* decay, float* o, float* state,
                              long long state_stride, const int* q_start, const int* q_len, const int* state_slot, int S,
                              int H, int dim, int vdim, cudaStream_t st) {
@@ -246,32 +359,27 @@ MB_API int mb_retention_scan(const float* q, const float* k, const float* v, con
     if (H < 1 || H > 65535 || S > 65535 || dim < 1 || dim > 256 || vdim < 1) return -2;
     const int cols = RT_THREADS / RT_LANES;
     const dim3 grid((vdim + cols - 1) / cols, H, S);
-#define RT_CASE(R)                                                                                                   \
-    if (dim <= R * RT_LANES) {                                                                                         \
-        retention_scan_kernel<R><<<grid, RT_THREADS, 0, st>>>(q, k, v, decay, o, state, state_stride, q_start, q_len,  \
-                                                              state_slot, H, dim, vdim);                               \
-        MB_LAUNCH_CHECK();                                                                                             \
-        return 0;                                                                                                      \
-    }
-    RT_CASE(2) RT_CASE(4) RT_CASE(8) RT_CASE(16) RT_CASE(32)
-#undef RT_CASE
-    return -2;
+    return RT_DISPATCH(0, grid, q, k, v, decay, o, state, state_stride, nullptr, q_start, q_len, state_slot, S, 0, H, dim, vdim,
+                       st);
 }
 
-MB_API int mb_retention_chunk(const float* q, const float* k, const float* v, const float* decay, float* o, float* state,
+// N tokens in S sequences make at most N / seg + S segments; carry (carry_rows, H vdim dim) must hold as many rows.
+MB_API int mb_retention_split(const float* q, const float* k, const float* v, const float* decay, float* o, float* state,
                               long long state_stride, const int* q_start, const int* q_len, const int* state_slot, int S,
-                              int H, int dim, int vdim, cudaStream_t st) {
-    if (S == 0) return 0;
-    if (H < 1 || H > 65535 || S > 65535 || dim < 1 || dim > RC_MAX_DIM || vdim < 1) return -2;
-    const size_t smem = ((size_t)dim * RC_COLS + 2 * RC_T * (dim + 1) + RC_T * RC_COLS + RC_T * (RC_T + 1) + RC_T + 1) * sizeof(float);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(retention_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
-    retention_chunk_kernel<<<dim3((vdim + RC_COLS - 1) / RC_COLS, H, S), RC_THREADS, smem, st>>>(
-        q, k, v, decay, o, state, state_stride, q_start, q_len, state_slot, H, dim, vdim);
+                              int N, int H, int dim, int vdim, int seg, float* carry, int carry_rows, cudaStream_t st) {
+    if (S == 0 || N == 0) return 0;
+    if (H < 1 || H > 65535 || S > 65535 || dim < 1 || dim > 256 || vdim < 1 || seg < 1) return -2;
+    const int most = N / seg + S;
+    if (most > carry_rows || most > 65535 || ((uintptr_t)carry & 15)) return -2;
+    const int cols = RT_THREADS / RT_LANES;
+    const dim3 grid((vdim + cols - 1) / cols, H, most);
+    int rc = RT_DISPATCH(1, grid, q, k, v, decay, o, state, state_stride, carry, q_start, q_len, state_slot, S, seg, H, dim,
+                         vdim, st);
+    if (rc) return rc;
+    const size_t per = (size_t)H * vdim * dim;
+    retention_carry_kernel<<<dim3((unsigned)((per + 255) / 256), S), 256, 0, st>>>(carry, decay, state, state_stride, q_len,
+                                                                                  state_slot, seg, H, dim, vdim);
     MB_LAUNCH_CHECK();
-    return 0;
+    return RT_DISPATCH(2, grid, q, k, v, decay, o, state, state_stride, carry, q_start, q_len, state_slot, S, seg, H, dim,
+                       vdim, st);
 }

@@ -458,18 +458,38 @@ def retention_prep(rows, q_off, k_off, v_off, positions, freqs, q, k, v, H, dim,
              rows.shape[0], H, dim, vdim, int(rotary_dim), float(k_scale), _stream()), "retention_prep")
 
 
-RETENTION = {"chunk_tokens": 64}        # steps with more tokens than this run the chunk form of the recurrence
+# steps with more than `chunk_tokens` tokens a sequence run the split form of the recurrence, in segments of `segment_tokens`
+RETENTION = {"chunk_tokens": 64, "segment_tokens": 128}
 
 
-def retention(q, k, v, decay, o, state, seq, H, dim, vdim, chunked=False):
+def retention_carry_rows(N, S, segment=None):
+    """rows of the carry buffer that the split form wants for N tokens in S sequences"""
+    return N // int(segment or RETENTION["segment_tokens"]) + S
+
+
+def retention(q, k, v, decay, o, state, seq, H, dim, vdim, chunked=False, segment=None, carry=None):
     """Per sequence and head, token by token: S <- decay[h] S + k v^T; o = S^T q.  q, k (N, H, dim), v, o (N, H, vdim)
     float32; decay (H,) float32; state (slots, >= H vdim dim) float32, a head's state stored (vdim, dim);
-    seq = (q_start, q_len, state_slot) device arrays.  chunked: the form that works a stretch of tokens side by side."""
+    seq = (q_start, q_len, state_slot) device arrays.  chunked: the split form, which cuts every sequence into segments of
+    `segment` tokens that run side by side; carry (>= retention_carry_rows(N, S, segment), H vdim dim) float32 is its
+    scratch (made here when absent)."""
     _cuda(q, k, v, decay, o, state, *seq)
-    f = _fn("retention", "mb_retention_chunk" if chunked else "mb_retention_scan",
-            [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
-    _check(f(_p(q), _p(k), _p(v), _p(decay), _p(o), _p(state), state.stride(0), _p(seq[0]), _p(seq[1]), _p(seq[2]),
-             seq[0].numel(), H, dim, vdim, _stream()), "retention")
+    if not chunked:
+        f = _fn("retention", "mb_retention_scan", [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
+        _check(f(_p(q), _p(k), _p(v), _p(decay), _p(o), _p(state), state.stride(0), _p(seq[0]), _p(seq[1]), _p(seq[2]),
+                 seq[0].numel(), H, dim, vdim, _stream()), "retention")
+        return
+    import torch
+    N, S = q.shape[0], seq[0].numel()
+    segment = int(segment or RETENTION["segment_tokens"])
+    if carry is None:
+        carry = torch.empty(retention_carry_rows(N, S, segment), H * vdim * dim, dtype=torch.float32, device=q.device)
+    _cuda(carry)
+    f = _fn("retention", "mb_retention_split",
+            [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 6 + [c_void_p, c_int, c_void_p])
+    _check(f(_p(q), _p(k), _p(v), _p(decay), _p(o), _p(state), state.stride(0), _p(seq[0]), _p(seq[1]), _p(seq[2]), S, N, H,
+             dim, vdim, segment, _p(carry), carry.shape[0], _stream()), "retention")
+    COUNTERS["launches"] += 2           # the first pass, the carry, the second pass
 
 
 # ------------------------------------------------------------------------------------------------ attention with sigmoid weights

@@ -9,7 +9,7 @@
 The layer keeps nothing per position; per request it keeps S (heads, vdim, dim) in float32, zeroed when a request takes
 its state slot.  A step: one product of the mixer's input (q, k, v and the gate side by side), one kernel that rotates
 and leaves q, k, v in float32, the recurrence (a sequence's tokens in order, whatever their number: prompts, portions and
-single tokens; long stretches in the form that works a chunk of tokens side by side), the gated norm of its output,
+single tokens; long stretches cut into segments that run side by side), the gated norm of its output,
 the output product.  Angles, the state, the recurrence and the norm are float32.
 """
 from ..cache.manager import StateNeed
@@ -88,8 +88,12 @@ class Retention:
         state = ctx.cache.state[run.state_id][:, off:off + self.state_floats()]
         # the number of tokens per sequence follows from the lengths of the step's arrays (N tokens, S sequences)
         chunked = N > ops.RETENTION["chunk_tokens"] * ctx.S and not ctx.options.get("retention_scan_only", False)
+        carry = None
+        if chunked:             # a row per segment, each a whole state: reserved for the largest step's segments, not its tokens
+            carry = ctx.ws.get("retention_carry", ops.retention_carry_rows(N, ctx.S), (H * vdim * dim,), f32,
+                               reserve=ops.retention_carry_rows(ctx.ws.max_rows, ctx.S))
         ops.retention(q, k, v, self.decay, o, state, (ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("state_slot")), H, dim,
-                      vdim, chunked=chunked)
+                      vdim, chunked=chunked, carry=carry)
         a = ctx.ws.get("retention_gated", N, (H * vdim,), ctx.dtype)
         ops.gated_rms(o, rows[:, 2 * H * dim + H * vdim:], None, a, H, vdim, self.eps, silu=True)
         y = ctx.ws.get(out, N, (self.D,), ctx.dtype)

@@ -49,11 +49,13 @@ def plain_recurrence(q, k, v, decay):
 
 
 @pytest.mark.parametrize("H,dim,vdim,decay", [(3, 16, 24, (0.5, 0.9, 1.0)), (2, 40, 20, (0.97, 0.999)), (1, 8, 72, (0.75,)),
-                                              (2, 64, 32, (1.0, 0.99)), (1, 128, 40, (0.995,)), (2, 10, 6, (0.8, 0.95))])
+                                              (2, 64, 32, (1.0, 0.99)), (1, 128, 40, (0.995,)), (2, 10, 6, (0.8, 0.95)),
+                                              (1, 200, 12, (0.9,))])
 def test_retention_carries_its_state_across_any_cut(H, dim, vdim, decay):
     """Three sequences advance side by side in portions of their own sizes (1 and 2 tokens among them, and stretches
-    long enough for the chunk form, whose chunks the cuts do not respect), in state slots that are not in order; the
-    state lies inside a wider tensor.  Both forms of the kernel, against the plain loop."""
+    long enough for the split form, whose segments the cuts do not respect), in state slots that are not in order; the
+    state lies inside a wider tensor, for an even number of heads off the 16-byte boundaries.  The scan and the split form
+    with segments of several sizes (most portions one segment, most portions many), against the plain loop."""
     from mashbox_b200 import ops
     g = torch.Generator().manual_seed(dim)
     T = 150
@@ -63,8 +65,8 @@ def test_retention_carries_its_state_across_any_cut(H, dim, vdim, decay):
         seqs.append((q, k, v) + plain_recurrence(q, k, v, decay))
     dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
     cuts = [[1, 1, 2, 33, 9, 70, 3, 31], [2, 97, 1, 7, 43], [65, 17, 1, 2, 64, 1]]
-    for chunked in (False, True):
-        pad, n = 40, H * dim * vdim
+    for chunked, segment in ((False, None), (True, None), (True, 16), (True, 7), (True, 1)):
+        pad, n = 40 + (H % 2 == 0), H * dim * vdim
         state = torch.zeros(5, pad + n + 8, device=DEV)
         slots = [3, 0, 4]
         at, got = [0, 0, 0], [[], [], []]
@@ -77,7 +79,7 @@ def test_retention_carries_its_state_across_any_cut(H, dim, vdim, decay):
             o = torch.full((sum(lens), H * vdim), float("nan"), device=DEV)
             q_start = np.concatenate([[0], np.cumsum(lens)[:-1]])
             ops.retention(q, k, v, dec, o, state[:, pad:pad + n], (i32(q_start), i32(lens), i32([slots[s] for s in live])),
-                          H, dim, vdim, chunked=chunked)
+                          H, dim, vdim, chunked=chunked, segment=segment)
             at_o = 0
             for s, n_ in zip(live, lens):
                 got[s].append(o[at_o:at_o + n_].cpu())
@@ -86,7 +88,7 @@ def test_retention_carries_its_state_across_any_cut(H, dim, vdim, decay):
         assert at == [T, T, T]
         for s in range(3):
             kernel_close(torch.cat(got[s]).reshape(T, H, vdim), seqs[s][3], "float32",
-                         f"retention ({'chunks' if chunked else 'scan'}), sequence {s}", 1e-5)
+                         f"retention ({f'segments of {segment}' if chunked else 'scan'}), sequence {s}", 1e-5)
             kept = state[slots[s], pad:pad + n].view(H, vdim, dim).transpose(1, 2)      # a head's state is stored (vdim, dim)
             kernel_close(kept, seqs[s][4], "float32", f"the state sequence {s} leaves", 1e-5)
         assert float(state[:, :pad].abs().max()) == 0.0 and float(state[:, pad + n:].abs().max()) == 0.0
@@ -101,12 +103,12 @@ def test_retention_keeps_a_far_token_only_as_its_decay_allows():
     q, k, v = torch.zeros(T, H, dim, dtype=F64), torch.zeros(T, H, dim, dtype=F64), torch.zeros(T, H, vdim, dtype=F64)
     k[20, :, 3], v[20, :, 5] = 2.0, 3.0
     q[620, :, 3] = 1.0
-    for chunked in (False, True):
+    for chunked, segment in ((False, None), (True, None), (True, 100), (True, 256)):
         state = torch.zeros(1, H * dim * vdim, device=DEV)
         o = torch.empty(T, H * vdim, device=DEV)
         dev = lambda x: x.reshape(T, -1).float().to(DEV).contiguous()
         ops.retention(dev(q), dev(k), dev(v), torch.tensor(decay, device=DEV), o, state, (i32([0]), i32([T]), i32([0])), H, dim,
-                      vdim, chunked=chunked)
+                      vdim, chunked=chunked, segment=segment)
         o = o.view(T, H, vdim).cpu().double()
         want = torch.tensor([6.0 * d ** 600 for d in decay], dtype=F64)
         assert torch.allclose(o[620, :, 5], want, rtol=1e-4, atol=1e-30), (chunked, o[620, :, 5])
