@@ -1023,6 +1023,12 @@ def tosevik_kernels(a, z, P, B, ctx, pk):
                 res[f"{name}_prompt"] = mat(us, 4 * H * dim * P * P / 2)
                 if core is sig:             # a weight goes into the second product as two bf16 numbers: 3 products, not 2
                     res[f"{name}_prompt"]["tflops_issued"] = 6 * H * dim * P * P / 2 / us / 1e6
+                    # the same on mma.sync tiles (the form that takes every pair of head sizes)
+                    ctx_m = _PlanContext(ops, dev, q_len, [klen - n for n in q_len], page, pages, err)
+                    ctx_m.options["attention_prefill_kernel"] = "mma"
+                    core.prepare(ctx_m)
+                    ctx_m.inputs.upload()
+                    res[f"{name}_mma_prompt"] = mat(timed(lambda: core.attend(ctx_m, q, o, table, kp, vp)), 4 * H * dim * P * P / 2)
             else:
                 res[f"{name}_decode"] = mem(us, nbytes)
         if core is sig:                      # the kernel in front of it: norms over whole rows, temperature, cache write

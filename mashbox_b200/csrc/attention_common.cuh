@@ -31,6 +31,9 @@ struct AttnParams {
     // the differential form of the tcgen05 kernel (two maps per head over one set of values): `window` is then the size of
     // the block of positions a query sees, and the output row is (a_0 - diff_lam a_1) / rms * diff_gain
     float diff_lam = 0.0f, diff_gain = 1.0f, diff_eps = 0.0f;
+    // the form of the tcgen05 kernel whose weights are sigmoids: a distance slope and a bias per query head (null: 0)
+    const float* sig_slopes = nullptr;
+    const float* sig_bias = nullptr;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {

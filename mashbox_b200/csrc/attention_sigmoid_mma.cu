@@ -81,6 +81,15 @@ __device__ __forceinline__ void sig_load_tile(bf16* stage, const SigParams& P, c
     }
 }
 
+// sigmoid(z) = 1 / (1 + 2^(-z log2 e)) with the special-function unit's 2^x and reciprocal (a few ulp each, no slow
+// path and no branch; 2^x = inf for a far negative z gives 0)
+__device__ __forceinline__ float sig_unit(float z) {
+    float e, w;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(w) : "f"(1.0f + e));
+    return w;
+}
+
 // the weights of one 16 x 8 score tile: s holds q . k, rows gq (e = 0, 1) and gq + 8 (e = 2, 3), keys key0 + (e & 1)
 __device__ __forceinline__ void sig_weights(float (&s)[4], int key0, const int (&rpos)[2], const float (&slope)[2],
                                             const float (&bias)[2], float scale) {
@@ -88,7 +97,7 @@ __device__ __forceinline__ void sig_weights(float (&s)[4], int key0, const int (
     for (int e = 0; e < 4; e++) {
         const int i = e >> 1, key = key0 + (e & 1);
         const float z = fmaf(s[e], scale, bias[i]) - slope[i] * (float)(rpos[i] - key);
-        s[e] = key <= rpos[i] ? __frcp_rn(1.0f + __expf(-z)) : 0.0f;
+        s[e] = key <= rpos[i] ? sig_unit(z) : 0.0f;
     }
 }
 

@@ -31,6 +31,12 @@
 // products read the one value tile, and at the end the warpgroup of map 1 hands its rows' 1 / sum over and the
 // warpgroup of map 0 reads both accumulators and writes (a_0 - lam a_1) / rms * gain.  `window` is the size of the block
 // of positions a query sees (blocks counted from position 0; 0: every earlier key) instead of a sliding window.
+// Compiled with -DT5_SIG the weights are SIGMOIDS and nothing is normalised over the keys: a visible key j weighs
+// sigmoid(scale q_i . k_j - slope_h (i - j) + bias_h) for the query at position i, with a slope and a bias per query head.
+// There is no maximum, no sum and nothing to rescale: the row's warpgroup turns the 128 scores into weights (float32,
+// 2^x and the reciprocal on the special-function unit) and hands each to the output product as TWO bf16 numbers,
+// w = hi + lo, hi in the first 64 columns of the score buffer and lo in the last 64; the output product runs over both.
+// The weights of hundreds of keys add up with nothing to divide them by, so they keep 16 bits of mantissa.
 #ifdef T5_DIFF
 #define T5_ROWS T5_BM
 #else
@@ -47,6 +53,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 1 / (1 + 2^x): both steps on the special-function unit (2^x = inf for a far key gives 0)
+__device__ __forceinline__ float sig_weight(float x) {
+    float w;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(w) : "f"(1.0f + fast_exp2(x)));
+    return w;
 }
 
 // Two floats in one 64-bit register pair and the packed arithmetic on them (one issue slot for two results); a maximum
@@ -316,6 +329,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                     for (int kk = 0; kk < 8; kk++)                  // 16 keys per step: 2,048 bytes further in the tile
                         umma_f16_ts(tm_o0 + g * HD, tm_s0 + g * 128 + kk * 8, umma_desc_join(v_lo + kk * 128), idesc_pv,
                                     (t > 0 || kk > 0) ? 1u : 0u);
+#ifdef T5_SIG
+#pragma unroll
+                    for (int kk = 0; kk < 8; kk++)                  // the low parts of the weights, from the last 64 columns
+                        umma_f16_ts(tm_o0 + g * HD, tm_s0 + g * 128 + 64 + kk * 8, umma_desc_join(v_lo + kk * 128), idesc_pv, 1u);
+#endif
                     if (last_reader(g, t)) umma_commit(v_empty0 + 8 * s);
                     if (t == U.tiles(g) - 1) umma_commit(o_done0 + 8 * g);
                     return true;
@@ -402,7 +420,15 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 rlo = (P.window > 0 && rpos - P.window + 1 > 0) ? rpos - P.window + 1 : 0;
 #endif
             }
+#ifndef T5_SIG
             float m_run = -INFINITY, l_run = 0.0f;
+#else
+            // the row's head: slope and bias in units of log2 e, as the exponent of 2^x wants them
+            const int hq = kvh * G + (r < R ? r % G : 0);
+            const float sl2 = P.sig_slopes ? P.sig_slopes[hq] * 1.4426950408889634f : 0.0f;
+            const float bi2 = P.sig_bias ? P.sig_bias[hq] * 1.4426950408889634f : 0.0f;
+            const float nscale = -P.scale_log2;
+#endif
             for (int t = 0; t < Tq && ok; t++) {
                 // the scores of this tile are complete -- and so is every product issued before them: the output product
                 // of the tile before, which read the probabilities in this buffer and wrote the accumulator
@@ -422,6 +448,37 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
 #pragma unroll
                 for (int c = 0; c < 4; c++) tmem_ld32(s_addr + c * 32, sv[c]);
                 tmem_ld_wait();
+#ifdef T5_SIG
+                // weight = 1 / (1 + 2^x) with x = -z log2 e = s (-scale log2 e) + c0 - slope' i for the key kb + i, where
+                // c0 = slope' (rpos - kb) - bias'.  c0 is rounded once; where that rounding is large (far keys under a
+                // steep slope) the weight has long since vanished.  Keys after the row's position weigh nothing.
+                const int lim = rpos - kb;
+                const float c0 = fmaf(sl2, (float)lim, -bi2);
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) {
+                    uint32_t whi[32], wlo[32];
+#pragma unroll
+                    for (int cc = 0; cc < 2; cc++) {
+                        const int c = hf * 2 + cc;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const int ka = c * 32 + i;
+                            float wa = sig_weight(fmaf(__uint_as_float(sv[c][i]), nscale, fmaf(sl2, -(float)ka, c0)));
+                            float wb = sig_weight(fmaf(__uint_as_float(sv[c][i + 1]), nscale, fmaf(sl2, -(float)(ka + 1), c0)));
+                            if (!full_tile) {
+                                if (ka > lim) wa = 0.0f;
+                                if (ka + 1 > lim) wb = 0.0f;
+                            }
+                            const uint32_t h2 = pack_bf16(wa, wb);
+                            whi[cc * 16 + (i >> 1)] = h2;
+                            wlo[cc * 16 + (i >> 1)] = pack_bf16(wa - __uint_as_float(h2 << 16), wb - __uint_as_float(h2 & 0xffff0000u));
+                        }
+                    }
+                    tmem_st32(s_addr + hf * 32, whi);
+                    tmem_st32(s_addr + 64 + hf * 32, wlo);
+                }
+                tmem_st_wait();
+#else
                 // eight running maxima (and eight partial sums below): one chain of 128 dependent operations would cost
                 // its latency 128 times over
                 float mxs[8];
@@ -506,6 +563,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 for (int i = 0; i < 4; i++) unpack2(sums2[i], sums[2 * i], sums[2 * i + 1]);
                 const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
                 l_run = l_run * corr + sum;
+#endif
                 tc_fence_before();
                 mbar_arrive(p_full0 + 8 * g);
             }
@@ -576,7 +634,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
             }
 #else
             {
+#ifdef T5_SIG
+                const float inv = 1.0f;                             // the plain weighted sum
+#else
                 const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#endif
                 const bool live_row = r < R;                        // rows past the end take part in the loads only
                 bf16* dst = P.out + (live_row ? ((size_t)(tok0 + r / G) * P.H + (kvh * G + r % G)) * HD : 0);
 #pragma unroll 1
@@ -665,8 +727,10 @@ static int launch_tc5(const AttnParams& P, const CUtensorMap& kmap, const CUtens
 }
 
 // items: (sequence, tile of T5_ROWS packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
-#ifdef T5_DIFF
+#if defined(T5_DIFF)
 #define T5_ENTRY mb_attn_tc5_diff_bf16
+#elif defined(T5_SIG)
+#define T5_ENTRY mb_attn_tc5_sig_bf16
 #else
 #define T5_ENTRY mb_attn_tc5_bf16
 #endif
@@ -677,12 +741,18 @@ MB_API int T5_ENTRY(const void* q, int q_stride, void* out, const void* kpool, c
 #ifdef T5_DIFF
                             float lam, float gain, float eps,
 #endif
+#ifdef T5_SIG
+                            const float* slopes, const float* bias,             // per query head, or null (0)
+#endif
                             int* err, cudaStream_t st) {
     if (n_items == 0) return 0;
     if (!mb_attn_tc5_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
     AttnParams P;
 #ifdef T5_DIFF
     P.diff_lam = lam; P.diff_gain = gain; P.diff_eps = eps;
+#endif
+#ifdef T5_SIG
+    P.sig_slopes = slopes; P.sig_bias = bias;
 #endif
     P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
     P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;

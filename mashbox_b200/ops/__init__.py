@@ -566,6 +566,31 @@ def sigmoid_attention_mma_decode(q, out, items, n_items, slots, n_slots, part_o,
         COUNTERS["launches"] += 1
 
 
+def sigmoid_attention_tc5_supports(dim, vdim, page):
+    """the tcgen05 kernel's form with sigmoid weights: keys and values of one width, 64 or 128"""
+    return dim == vdim and attention_tc5_supports(dim, page)
+
+
+def sigmoid_attention_tc5_rows():
+    """packed query rows of one work item of the tcgen05 kernel (two query tiles of 128 rows share the K and V tiles)"""
+    return 256
+
+
+def sigmoid_attention_tc5(q, out, items, n_items, q_start, q_len, pos0, seq_row, table, kpool, vpool, slopes, bias, H, G, dim,
+                          vdim, page, num_pages, scale, err):
+    """The prompt form of the attention with sigmoid weights on tcgen05 (the result of sigmoid_attention_simple): items
+    are n_items (sequence, tile of 256 packed rows, 0, 1) quadruples, heaviest first."""
+    _cuda(q, out, items, q_start, q_len, pos0, seq_row, table, kpool, vpool, slopes, bias)
+    if q.dtype != torch.bfloat16 or not sigmoid_attention_tc5_supports(dim, vdim, page):
+        raise KernelError(f"sigmoid_attention_tc5: no kernel for {q.dtype}, head sizes {dim} and {vdim}, pages of {page}")
+    f = _fn("attention_tc5_sig", "mb_attn_tc5_sig_bf16",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int] + [c_int] * 6 + [c_float] + [c_void_p] * 4)
+    _check(f(_p(q), H * dim, _p(out), _p(kpool), _p(vpool), _p(items), int(n_items), _p(q_start), _p(q_len), _p(pos0),
+             _p(seq_row), _p(table), table.shape[1], H, G, dim, page, num_pages, 0, float(scale), _p(slopes), _p(bias),
+             _p(err), _stream()), "sigmoid_attention_tc5")
+
+
 # ------------------------------------------------------------------------------------------------ routed experts
 def moe_select(z, correction, ids, wts, groups=1, keep=1, experts=None, softmax=False, worth="top2", scale=1.0):
     """z (N, >= E) float32 router logits (E = experts, default: every column) -> ids (N, top) int32, wts (N, top) float32:

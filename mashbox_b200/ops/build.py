@@ -46,6 +46,7 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "attention_tma": ("attention_tma.cu", []),
     "attention_tc5": ("attention_tc5.cu", []),
     "attention_tc5_diff": ("attention_tc5.cu", ["-DT5_DIFF"]),         # two maps per head over one set of values
+    "attention_tc5_sig": ("attention_tc5.cu", ["-DT5_SIG"]),           # sigmoid weights, nothing normalised over the keys
     "sampling": ("sampling.cu", []),
     "sampling_noalloc": ("sampling_noalloc.cu", []),
     "trace": ("trace.cu", []),

@@ -14,8 +14,9 @@ scores, weights and sums are float32.
 
 Kernels: the float32 path, and head sizes that are no multiples of 16 up to 128, use the plain kernel (a warp per token
 and head, keys in ascending order).  The bfloat16 path packs the query heads of a kv head into the rows of an MMA tile:
-tiles of 64 rows for prompt portions, tiles of 16 with the keys split over warps and over blocks for decode tokens;
-`prepare` builds both work lists on the host.  A weight reaches the second product as two bfloat16 numbers (hi + lo).
+tiles of 64 rows for prompt portions (on tcgen05, two tiles of 128 rows that share the keys, when keys and values are both
+64 or both 128 wide), tiles of 16 with the keys split over warps and over blocks for decode tokens; `prepare` builds both
+work lists on the host.  A weight reaches the second product as two bfloat16 numbers (hi + lo).
 """
 import numpy as np
 
@@ -81,9 +82,14 @@ class SigmoidAttention:
         return (ctx.dtype == torch.bfloat16 and ctx.ops.sigmoid_attention_mma_supports(self.dim, self.vdim)
                 and not ctx.options.get("plain_attention", False))
 
+    def uses_tc5(self, ctx):
+        """prompt-form tiles go to the tcgen05 kernel when keys and values are both 64 or both 128 wide"""
+        return (ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
+                and ctx.ops.sigmoid_attention_tc5_supports(self.dim, self.vdim, ctx.cache.page_size))
+
     def plan_key(self):
-        # everything the work lists depend on (layers with the same grouping of heads share them)
-        return ("sigmoid_attention", self.H // self.G, self.G)
+        # everything the work lists depend on (the head sizes decide the kernel and its rows per tile)
+        return ("sigmoid_attention", self.H // self.G, self.G, self.dim, self.vdim)
 
     def prepare(self, ctx):
         """host side, for the tensor-core kernels: the lists of (sequence, row tile) work items of the prompt form and
@@ -95,12 +101,15 @@ class SigmoidAttention:
             return
         ops = ctx.ops
         name = "sig%d_" % len([k for k in ctx.memo if k[0] == "sigmoid_attention"])
-        plan = plan_diff_attention(ctx.q_len, ctx.pos0, self.H // self.G, self.G, None, ops.SIGMOID_MMA_ROWS,
+        tc5 = self.uses_tc5(ctx)
+        plan = plan_diff_attention(ctx.q_len, ctx.pos0, self.H // self.G, self.G, None,
+                                   ops.sigmoid_attention_tc5_rows() if tc5 else ops.SIGMOID_MMA_ROWS,
                                    ops.SIGMOID_DECODE_ROWS, ops.SIGMOID_MAX_SPLITS,
-                                   int(ctx.options.get("attention_target_blocks", 296)), ctx.options.get("attention_splits"))
+                                   int(ctx.options.get("attention_target_blocks", 296)), ctx.options.get("attention_splits"),
+                                   quads=tc5)
         for k, v in plan.items():
             ctx.inputs.add(name + k, np.asarray(v, np.int32))
-        ctx.memo[key] = dict(name=name, n_pre=len(plan["pre"]) // 2, n_dec=len(plan["dec"]) // 4,
+        ctx.memo[key] = dict(name=name, tc5=tc5, n_pre=len(plan["pre"]) // (4 if tc5 else 2), n_dec=len(plan["dec"]) // 4,
                              n_slots=len(plan["slots"]) // 2)
 
     def forward(self, ctx, h, run, out="delta"):
@@ -135,7 +144,8 @@ class SigmoidAttention:
         seqs = (ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"))
         tail = (table, kpool, vpool, self.slopes, self.pb, H, G, dim, vdim, page, pages, self.scale, ctx.err)
         if plan["n_pre"]:
-            ops.sigmoid_attention_mma(q, o, ctx.dev(nm + "pre"), plan["n_pre"], *seqs, *tail)
+            prompt_form = ops.sigmoid_attention_tc5 if plan["tc5"] else ops.sigmoid_attention_mma
+            prompt_form(q, o, ctx.dev(nm + "pre"), plan["n_pre"], *seqs, *tail)
         if plan["n_dec"]:
             part_o = None
             if plan["n_slots"]:

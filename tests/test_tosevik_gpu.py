@@ -253,7 +253,8 @@ def test_experts_sum_with_a_gated_shared_expert(dtype):
 # ------------------------------------------------------------------------------------------------ attention with sigmoid weights
 def sigmoid_case(dtype, H, G, dim, vdim, lengths, q_lens, page, loud, kernel, temp=None, seed=0, pb=-4.0, scale=None):
     """Sequences whose keys and values the prep kernel writes into shuffled pages (a step of whole prompts), then a step
-    whose queries are each sequence's last q_lens tokens, attended by `kernel` ("plain" or "mma").  loud: (sequence, key
+    whose queries are each sequence's last q_lens tokens, attended by `kernel` ("plain", "mma", or "tc5": the prompt
+    form on tcgen05).  loud: (sequence, key
     position, query position): the query's row points along that key's row (all heads), so that the one score stands
     out wherever the query may see the key.  -> the kernel's output rows and the plain answer"""
     from mashbox_b200 import ops
@@ -310,12 +311,16 @@ def sigmoid_case(dtype, H, G, dim, vdim, lengths, q_lens, page, loud, kernel, te
                                      scale, err)
     else:
         pos0 = [n - ql for n, ql in zip(lengths, q_lens)]
-        plan = plan_diff_attention(q_lens, pos0, H // G, G, None, ops.SIGMOID_MMA_ROWS, ops.SIGMOID_DECODE_ROWS,
-                                   ops.SIGMOID_MAX_SPLITS, 296, kernel[1] if isinstance(kernel, tuple) else None)
+        tc5 = kernel == "tc5"
+        plan = plan_diff_attention(q_lens, pos0, H // G, G, None, ops.sigmoid_attention_tc5_rows() if tc5 else ops.SIGMOID_MMA_ROWS,
+                                   ops.SIGMOID_DECODE_ROWS, ops.SIGMOID_MAX_SPLITS, 296,
+                                   kernel[1] if isinstance(kernel, tuple) else None, quads=tc5)
         q_start = i32(np.concatenate([[0], np.cumsum(q_lens)[:-1]]))
         seqs = (q_start, i32(q_lens), i32(pos0), i32(seq_rows))
         tail = (table, kpool, vpool, slopes, pbd, H, G, dim, vdim, page, num_pages, scale, err)
-        if plan["pre"]:
+        if plan["pre"] and tc5:
+            ops.sigmoid_attention_tc5(q, o, i32(plan["pre"]), len(plan["pre"]) // 4, *seqs, *tail)
+        elif plan["pre"]:
             ops.sigmoid_attention_mma(q, o, i32(plan["pre"]), len(plan["pre"]) // 2, *seqs, *tail)
         if plan["dec"]:
             n_slots = len(plan["slots"]) // 2
@@ -328,7 +333,8 @@ def sigmoid_case(dtype, H, G, dim, vdim, lengths, q_lens, page, loud, kernel, te
 
 SIG_SHAPES = [("plain", 4, 2, 16, 24, 8), ("plain", 3, 1, 12, 20, 5), ("plain", 2, 2, 40, 8, 16),
               ("mma", 4, 2, 16, 32, 8), ("mma", 8, 2, 64, 64, 16), ("mma", 2, 1, 128, 32, 64), ("mma", 3, 3, 32, 128, 5),
-              ("mma", 32, 1, 16, 16, 16)]
+              ("mma", 32, 1, 16, 16, 16), ("tc5", 8, 2, 64, 64, 16), ("tc5", 4, 1, 128, 128, 32), ("tc5", 3, 3, 64, 64, 8),
+              ("tc5", 12, 2, 128, 128, 128)]
 
 
 @pytest.mark.parametrize("kernel,H,G,dim,vdim,page", SIG_SHAPES)
