@@ -979,12 +979,17 @@ def tosevik_kernels(a, z, P, B, ctx, pk):
         state = torch.zeros(S, H * dim * dim, device=dev)
         seq = (i32([i * (N // S) for i in range(S)]), i32([N // S] * S), i32(list(range(S))))
         nbytes = 2 * S * H * dim * dim * 4 + N * H * dim * 4 * 4
-        for name, chunked in (("retention", form == "prompt"), ("retention_scan", False)):
+        for name, chunked in (("retention_split", True), ("retention_scan", False)):
+            if chunked and form == "decode":
+                continue
             us = timed(lambda: ops.retention(q, k, v, decay, o, state, seq, H, dim, dim, chunked=chunked))
             r = mem(us, nbytes)
             r["gflops_fp32"] = N * H * dim * dim * 4 / us / 1e3                  # decay + write, read: 4 per element and token
             res[f"{name}_{form}"] = r
             state.zero_()
+        # the form the mixer takes at this size
+        picked = "retention_split" if ops.retention_splits(N, S, H, dim) else "retention_scan"
+        res[f"retention_{form}"] = dict(res[f"{picked}_{form}"], form=picked)
         g, beta = torch.rand(N, H * dim, generator=gen, device=dev), torch.rand(N, H, generator=gen, device=dev)
         us = timed(lambda: ops.delta_rule(q, k, v, g, beta, o, state, seq, H, H, dim, dim))
         res[f"delta_rule_sufopel_{form}"] = mem(us, nbytes + N * H * dim * 4)

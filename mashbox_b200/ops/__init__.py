@@ -458,8 +458,20 @@ def retention_prep(rows, q_off, k_off, v_off, positions, freqs, q, k, v, H, dim,
              rows.shape[0], H, dim, vdim, int(rotary_dim), float(k_scale), _stream()), "retention_prep")
 
 
-# steps with more than `chunk_tokens` tokens a sequence run the split form of the recurrence, in segments of `segment_tokens`
-RETENTION = {"chunk_tokens": 64, "segment_tokens": 128}
+# Steps with more than `chunk_tokens` tokens a sequence run the split form of the recurrence, in segments of
+# `segment_tokens` -- when the scan would leave the device short of blocks (fewer than `scan_blocks`): the split form walks
+# every token twice, which pays only while the scan's blocks do not fill the multiprocessors.
+RETENTION = {"chunk_tokens": 64, "segment_tokens": 128, "scan_blocks": 148}
+
+
+def retention_scan_blocks(S, H, vdim):
+    """blocks of the scan form: a block takes 16 columns of one head's state of one sequence"""
+    return S * H * (-(-vdim // 16))
+
+
+def retention_splits(N, S, H, vdim):
+    """whether a step of N tokens in S sequences runs the split form"""
+    return N > RETENTION["chunk_tokens"] * S and retention_scan_blocks(S, H, vdim) < RETENTION["scan_blocks"]
 
 
 def retention_carry_rows(N, S, segment=None):

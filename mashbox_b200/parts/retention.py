@@ -87,7 +87,7 @@ class Retention:
         off = self.state_offset
         state = ctx.cache.state[run.state_id][:, off:off + self.state_floats()]
         # the number of tokens per sequence follows from the lengths of the step's arrays (N tokens, S sequences)
-        chunked = N > ops.RETENTION["chunk_tokens"] * ctx.S and not ctx.options.get("retention_scan_only", False)
+        chunked = ops.retention_splits(N, ctx.S, H, vdim) and not ctx.options.get("retention_scan_only", False)
         carry = None
         if chunked:             # a row per segment, each a whole state: reserved for the largest step's segments, not its tokens
             carry = ctx.ws.get("retention_carry", ops.retention_carry_rows(N, ctx.S), (H * vdim * dim,), f32,

@@ -201,8 +201,10 @@ def test_dynamic_tanh_and_depth_average(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D", [64, 100])
+@pytest.mark.parametrize("D", [64, 100, 2056, 8192, 8200])
 def test_two_normed_outputs_halved(dtype, D):
+    """widths of one 16-byte piece a thread, of none for most threads, of four (the widest row the bf16 kernel keeps in
+    registers), and beyond it"""
     from mashbox_b200 import ops
     g = torch.Generator().manual_seed(D)
     N, eps = 5, 1e-2
@@ -560,11 +562,13 @@ def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(tmp_path_
 @pytest.mark.parametrize("name,dtype,options", [("V", "bfloat16", dict(plain_attention=True)),
                                                 ("V", "bfloat16", dict(retention_scan_only=True)),
                                                 ("V", "bfloat16", dict(attention_splits=4)),
+                                                ("V", "bfloat16", dict(attention_prefill_kernel="mma")),
                                                 ("V", "bfloat16", dict(plain_experts=True)),
                                                 ("T", "float32", dict(retention_scan_only=True))])
 def test_every_kernel_form_gives_the_same_model(tmp_path_factory, name, dtype, options):
     """the forms the engine chooses between by the step's size, forced: the plain attention kernel beside the
-    tensor-core one, the token-by-token recurrence beside the chunk form, decode keys cut four ways, experts pair by pair"""
+    tensor-core one, the token-by-token recurrence beside the split form, decode keys cut four ways, prompt tiles on
+    mma.sync where heads of 64 x 64 would take tcgen05, experts pair by pair"""
     folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 512, options=options)
     (p,) = S.prompts_for(name, (300,), seed=7)
     want = S.plain_logits(folder, p)
