@@ -53,32 +53,36 @@ constexpr size_t DSMEM_BYTES = (size_t)DBM * KROW * sizeof(bf16)
 static_assert(SIG_DIM % 16 == 0 && SIG_VD % 16 == 0 && SIG_DIM >= 16 && SIG_VD >= 16, "head sizes are multiples of 16");
 static_assert(SIG_DIM <= 128 && SIG_VD <= 128, "head sizes up to 128");
 
-// One tile of 64 keys and their values into a stage; rows at or beyond `hi` are filled with zeros.
+// One tile of 64 keys and their values into a stage; rows at or beyond `hi` are filled with zeros.  Two threads share a
+// row: its page, slot and addresses are worked out once, then the pair walks the row's 16-byte pieces side by side (a
+// whole 32-byte sector per pair and instruction), the key's first, then the value's.
 __device__ __forceinline__ void sig_load_tile(bf16* stage, const SigParams& P, const int* tb, int g, int kb, int hi, int tid) {
-    constexpr int CK = SIG_DIM / 8, CV = SIG_VD / 8, CT = CK + CV;
-    int last_block = -1, pg = -1;
-#pragma unroll
-    for (int cid = tid; cid < BN * CT; cid += THREADS) {
-        const int row = cid / CT, c = cid % CT;
-        const int kp = kb + row;
-        const bf16* src = P.kpool;
-        int bytes = 0;
-        if (kp < hi) {
-            int block, slot;
-            if (P.page_shift >= 0) { block = kp >> P.page_shift; slot = kp & (P.page - 1); }
-            else { block = kp / P.page; slot = kp - block * P.page; }
-            if (block != last_block) { pg = tb[block]; last_block = block; }
-            if (pg >= 0 && pg < P.num_pages) {
-                const size_t r = ((size_t)pg * P.G + g) * P.page + slot;
-                src = c < CK ? P.kpool + r * SIG_DIM + c * 8 : P.vpool + r * SIG_VD + (c - CK) * 8;
-                bytes = 16;
-            } else {
-                mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
-            }
+    constexpr int CK = SIG_DIM / 8, CV = SIG_VD / 8;
+    static_assert(THREADS == 2 * BN, "two threads a row");
+    const int row = tid >> 1, sub = tid & 1;
+    const int kp = kb + row;
+    const bf16* ksrc = P.kpool;
+    const bf16* vsrc = P.vpool;
+    int bytes = 0;
+    if (kp < hi) {
+        int block, slot;
+        if (P.page_shift >= 0) { block = kp >> P.page_shift; slot = kp & (P.page - 1); }
+        else { block = kp / P.page; slot = kp - block * P.page; }
+        const int pg = tb[block];
+        if (pg >= 0 && pg < P.num_pages) {
+            const size_t r = ((size_t)pg * P.G + g) * P.page + slot;
+            ksrc = P.kpool + r * SIG_DIM;
+            vsrc = P.vpool + r * SIG_VD;
+            bytes = 16;
+        } else {
+            mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
         }
-        bf16* dst = c < CK ? stage + swz<SIG_DIM>(row, c) : stage + BN * KROW + swz<SIG_VD>(row, c - CK);
-        cp_async16(dst, src, bytes);
     }
+    bf16* vstage = stage + BN * KROW;
+#pragma unroll
+    for (int c = 0; c < CK; c += 2) cp_async16(stage + swz<SIG_DIM>(row, c + sub), ksrc + (bytes ? (c + sub) * 8 : 0), bytes);
+#pragma unroll
+    for (int c = 0; c < CV; c += 2) cp_async16(vstage + swz<SIG_VD>(row, c + sub), vsrc + (bytes ? (c + sub) * 8 : 0), bytes);
 }
 
 // sigmoid(z) = 1 / (1 + 2^(-z log2 e)) with the special-function unit's 2^x and reciprocal (a few ulp each, no slow
