@@ -222,3 +222,15 @@ def test_plain_model_runs_and_depth_average_matters(tmp_path):
     q[20] = (q[20] + 1) % 131
     lg2 = plain.forward(cfg, W, q).numpy()
     assert np.abs(lg2[:20] - lg[:20]).max() < 1e-12 and np.abs(lg2[20:] - lg[20:]).max() > 1e-6
+
+
+def test_which_form_of_the_recurrence_a_step_takes():
+    """the split form walks every token twice: it is taken for long stretches only while the scan's blocks (sequences x
+    heads x 16 columns of the state) leave multiprocessors idle; its scratch is a state per segment"""
+    from mashbox_b200 import ops
+    assert ops.retention_scan_blocks(1, 16, 128) == 128 and ops.retention_scan_blocks(3, 2, 24) == 12
+    assert ops.retention_splits(2048, 1, 16, 128) and not ops.retention_splits(2048, 1, 24, 128)
+    assert not ops.retention_splits(2048, 2, 16, 128)                   # two sequences fill the device by themselves
+    assert not ops.retention_splits(64, 1, 2, 16) and ops.retention_splits(65, 1, 2, 16)
+    assert not ops.retention_splits(8, 8, 2, 16)                        # decode steps
+    assert ops.retention_carry_rows(300, 3) == 300 // 128 + 3 and ops.retention_carry_rows(300, 3, 7) == 300 // 7 + 3
