@@ -8,6 +8,7 @@
 //   rms_pair_mean   out[n] = (a[n] / rms(a[n]) * wa + b[n] / rms(b[n]) * wb) / 2: two outputs that ran side by side, each
 //                   normed over the whole row with a weight of its own
 #include "common.cuh"
+#include <initializer_list>
 
 template <typename T, typename OUT>
 __global__ void dyt_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ delta2, float alpha,
@@ -47,6 +48,94 @@ __global__ void depth_average_kernel(float* __restrict__ x, const T* __restrict_
     }
 }
 
+// ---- the forms for rows whose width is a multiple of 4: a thread takes 4 neighbours of one row (grid: rows x pieces of
+// 1,024 values), so nothing is divided and every access is 8 or 16 bytes wide
+struct F4 { float v[4]; };
+template <typename T> __device__ __forceinline__ F4 load4(const T* p);
+template <> __device__ __forceinline__ F4 load4<float>(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    return F4{{a.x, a.y, a.z, a.w}};
+}
+template <> __device__ __forceinline__ F4 load4<bf16>(const bf16* p) {
+    const uint2 a = *reinterpret_cast<const uint2*>(p);
+    return F4{{__uint_as_float(a.x << 16), __uint_as_float(a.x & 0xffff0000u), __uint_as_float(a.y << 16),
+               __uint_as_float(a.y & 0xffff0000u)}};
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const F4& a);
+template <> __device__ __forceinline__ void store4<float>(float* p, const F4& a) {
+    *reinterpret_cast<float4*>(p) = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, const F4& a) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(a.v[0], a.v[1]), pack_bf16(a.v[2], a.v[3]));
+}
+
+template <typename T, typename OUT>
+__global__ void __launch_bounds__(256)
+dyt4_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ delta2, float alpha,
+            const float* __restrict__ w, const float* __restrict__ b, OUT* out, const int* __restrict__ rows, int D) {
+    const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (d >= D) return;
+    const size_t n = blockIdx.x;
+    const size_t src = (rows ? (size_t)rows[n] : n) * D + d;
+    F4 v = load4<float>(x + src);
+    if (delta) {
+        const F4 a = load4<T>(delta + src);
+#pragma unroll
+        for (int e = 0; e < 4; e++) v.v[e] += a.v[e];
+        if (delta2) {
+            const F4 c = load4<T>(delta2 + src);
+#pragma unroll
+            for (int e = 0; e < 4; e++) v.v[e] += c.v[e];
+        }
+        if (!rows) store4<float>(x + src, v);
+    }
+    const F4 ww = load4<float>(w + d), bb = load4<float>(b + d);
+#pragma unroll
+    for (int e = 0; e < 4; e++) v.v[e] = tanhf(alpha * v.v[e]) * ww.v[e] + bb.v[e];
+    store4<OUT>(out + n * D + d, v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+depth_average4_kernel(float* __restrict__ x, const T* __restrict__ delta, float* __restrict__ hist, long long slot_stride,
+                      const float* __restrict__ coef, int idx, float nalpha, const float* __restrict__ nw,
+                      const float* __restrict__ nb, T* __restrict__ normed, int D) {
+    const int d = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (d >= D) return;
+    const size_t i = (size_t)blockIdx.x * D + d;
+    F4 v = load4<float>(x + i);
+    if (delta) {
+        const F4 a = load4<T>(delta + i);
+#pragma unroll
+        for (int e = 0; e < 4; e++) v.v[e] += a.v[e];
+    }
+    store4<float>(hist + (size_t)(idx + 1) * slot_stride + i, v);
+    F4 acc = F4{{0.0f, 0.0f, 0.0f, 0.0f}};
+    for (int j = 0; j <= idx; j++) {
+        const float c = coef[j];
+        const F4 h = load4<float>(hist + (size_t)j * slot_stride + i);
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc.v[e] = fmaf(c, h.v[e], acc.v[e]);
+    }
+    const float c = coef[idx + 1];
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc.v[e] = fmaf(c, v.v[e], acc.v[e]);
+    store4<float>(x + i, acc);
+    if (normed) {
+        const F4 ww = load4<float>(nw + d), bb = load4<float>(nb + d);
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc.v[e] = tanhf(nalpha * acc.v[e]) * ww.v[e] + bb.v[e];
+        store4<T>(normed + i, acc);
+    }
+}
+
+// every pointer on a 16-byte boundary, the width and the stride between history slots multiples of 4
+static bool rows_of_four(int D, long long stride, std::initializer_list<const void*> ptrs) {
+    if (D % 4 != 0 || stride % 4 != 0) return false;
+    for (const void* p : ptrs) if (((uintptr_t)p & 15) != 0) return false;
+    return true;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 rms_pair_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
@@ -68,10 +157,10 @@ rms_pair_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const flo
 
 // The bf16 form for rows of up to 8,192 values, a multiple of 8: a thread brings its 16-byte pieces of both rows in at
 // once and keeps them in registers between the sums of squares and the output, so every byte is read once.
+template <int MAXV>                     // 16-byte pieces a thread: rows of up to 2,048 MAXV values
 __global__ void __launch_bounds__(256)
 rms_pair_mean_rows_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, const float* __restrict__ wa,
                           const float* __restrict__ wb, bf16* __restrict__ out, int D, float eps) {
-    constexpr int MAXV = 4;
     __shared__ float scratch[32];
     const size_t n = blockIdx.x;
     const int nv = D >> 3;
@@ -127,7 +216,12 @@ bool pair_mean_rows<bf16>(const void* a, const void* b, const float* wa, const f
                           cudaStream_t st) {
     if (D % 8 != 0 || D > 8192) return false;
     if ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)out | (uintptr_t)wa | (uintptr_t)wb) & 15) != 0) return false;
-    rms_pair_mean_rows_kernel<<<N, 256, 0, st>>>((const bf16*)a, (const bf16*)b, wa, wb, (bf16*)out, D, eps);
+    if (D <= 2048)          // the fewer pieces a thread keeps, the more blocks a multiprocessor holds
+        rms_pair_mean_rows_kernel<1><<<N, 256, 0, st>>>((const bf16*)a, (const bf16*)b, wa, wb, (bf16*)out, D, eps);
+    else if (D <= 4096)
+        rms_pair_mean_rows_kernel<2><<<N, 256, 0, st>>>((const bf16*)a, (const bf16*)b, wa, wb, (bf16*)out, D, eps);
+    else
+        rms_pair_mean_rows_kernel<4><<<N, 256, 0, st>>>((const bf16*)a, (const bf16*)b, wa, wb, (bf16*)out, D, eps);
     return true;
 }
 
@@ -137,6 +231,17 @@ bool pair_mean_rows<bf16>(const void* a, const void* b, const float* wa, const f
         if (N == 0) return 0;                                                                                              \
         const long long total = (long long)N * D;                                                                          \
         const unsigned blocks = (unsigned)((total + 255) / 256);                                                           \
+        if (rows_of_four(D, 0, {x, delta, delta2, w, b, out})) {                                                           \
+            const dim3 grid(N, (D / 4 + 255) / 256);                                                                       \
+            if (out_float)                                                                                                 \
+                dyt4_kernel<T, float><<<grid, 256, 0, st>>>(x, (const T*)delta, (const T*)delta2, alpha, w, b,            \
+                                                            (float*)out, rows, D);                                         \
+            else                                                                                                           \
+                dyt4_kernel<T, T><<<grid, 256, 0, st>>>(x, (const T*)delta, (const T*)delta2, alpha, w, b, (T*)out, rows,  \
+                                                        D);                                                                \
+            MB_LAUNCH_CHECK();                                                                                             \
+            return 0;                                                                                                      \
+        }                                                                                                                  \
         if (out_float)                                                                                                     \
             dyt_kernel<T, float><<<blocks, 256, 0, st>>>(x, (const T*)delta, (const T*)delta2, alpha, w, b, (float*)out,  \
                                                          rows, D, total);                                                  \
@@ -151,6 +256,13 @@ bool pair_mean_rows<bf16>(const void* a, const void* b, const float* wa, const f
                                       cudaStream_t st) {                                                                   \
         if (N == 0) return 0;                                                                                              \
         if (idx < 0) return -2;                                                                                            \
+        if (rows_of_four(D, slot_stride, {x, delta, hist, nw, nb, normed})) {                                              \
+            depth_average4_kernel<T><<<dim3(N, (D / 4 + 255) / 256), 256, 0, st>>>(x, (const T*)delta, hist, slot_stride,  \
+                                                                                   coef, idx, nalpha, nw, nb, (T*)normed,  \
+                                                                                   D);                                     \
+            MB_LAUNCH_CHECK();                                                                                             \
+            return 0;                                                                                                      \
+        }                                                                                                                  \
         const long long total = (long long)N * D;                                                                          \
         depth_average_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, (const T*)delta, hist, slot_stride,    \
                                                                                  coef, idx, nalpha, nw, nb, (T*)normed, D, \

@@ -164,8 +164,9 @@ def test_unit_rms_heads_times_silu_gate(dtype):
 
 # ------------------------------------------------------------------------------------------------ the stream
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D", [64, 100, 257])
+@pytest.mark.parametrize("D", [64, 100, 257, 2052])
 def test_dynamic_tanh_and_depth_average(dtype, D):
+    """widths that take the four-wide kernels (one piece of a row, and two with a ragged end) and one that does not"""
     from mashbox_b200 import ops
     g = torch.Generator().manual_seed(D)
     N, L = 6, 4
