@@ -53,11 +53,15 @@ def _builtin():
     if _done:
         return
     _done = True
-    from ..models import llama, luzosun, sufopel, tosevik
+    from ..models import fipitar, llama, luzosun, sufopel, tosevik
+    from .fipitar import FipitarConfig
     from .llama import LlamaConfig
     from .luzosun import LuzosunConfig
     from .sufopel import SufopelConfig
     from .tosevik import TosevikConfig
+    if "Fipitar" not in ARCHITECTURES:
+        register_architecture(Architecture("Fipitar", FipitarConfig, fipitar.model_spec, fipitar.canonical_names,
+                                           fipitar.stored_tensors))
     if "Tosevik" not in ARCHITECTURES:
         register_architecture(Architecture("Tosevik", TosevikConfig, tosevik.model_spec, tosevik.canonical_names,
                                            tosevik.stored_tensors))

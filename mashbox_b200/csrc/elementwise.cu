@@ -663,3 +663,38 @@ MB_API int mb_swiglu_f32(const void* gu, void* out, int N, int F, cudaStream_t s
 MB_API int mb_swiglu_bf16(const void* gu, void* out, int N, int F, cudaStream_t st) {
     return swiglu_launch<__nv_bfloat16>(gu, out, N, F, st);
 }
+
+// ------------------------------------------------------------------------------------------------ clamped gated unit
+// gu[n] = [gate (F) | up (F)] -> out[n, f] = g sigmoid(alpha g) (u + shift), g = min(gate, limit) (clamped from above
+// only), u = clamp(up, -limit, limit); limit <= 0: no clamps.  The activation of the routed experts, for a dense layer.
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total, float limit,
+                                   float alpha, float shift) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / F, f = i % F;
+    float g = mb_load(gu + n * 2 * F + f), u = mb_load(gu + n * 2 * F + F + f);
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    mb_store(out + i, g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+template <typename T>
+static int glu_clamped_launch(const void* gu, void* out, int N, int F, float limit, float alpha, float shift,
+                              cudaStream_t st) {
+    const size_t total = (size_t)N * F;
+    if (total == 0) return 0;
+    glu_clamped_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)out, F, total, limit, alpha,
+                                                                           shift);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_glu_clamped_f32(const void* gu, void* out, int N, int F, float limit, float alpha, float shift,
+                              cudaStream_t st) {
+    return glu_clamped_launch<float>(gu, out, N, F, limit, alpha, shift, st);
+}
+MB_API int mb_glu_clamped_bf16(const void* gu, void* out, int N, int F, float limit, float alpha, float shift,
+                               cudaStream_t st) {
+    return glu_clamped_launch<__nv_bfloat16>(gu, out, N, F, limit, alpha, shift, st);
+}

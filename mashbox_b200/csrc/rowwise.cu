@@ -102,7 +102,7 @@ __global__ void rms_segments_kernel(const T* __restrict__ in, int stride, int of
                                     T* __restrict__ out_a, int off_b, int wb, const float* __restrict__ w_b, T* __restrict__ pool,
                                     const int* __restrict__ positions, const int* __restrict__ tok_row,
                                     const int* __restrict__ table, int max_blocks, int page, int num_pages, float eps,
-                                    int* err) {
+                                    int* err, int pool_row) {
     __shared__ float scratch[32];
     const int n = blockIdx.x, second = blockIdx.y;
     const int off = second ? off_b : off_a, W = second ? wb : wa;
@@ -118,7 +118,7 @@ __global__ void rms_segments_kernel(const T* __restrict__ in, int stride, int of
             if (threadIdx.x == 0) mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
             return;
         }
-        dst = pool + ((size_t)pg * page + p % page) * wb;
+        dst = pool + ((size_t)pg * page + p % page) * pool_row;       // a row may be wider than the stretch
     }
     const T* src = in + (size_t)n * stride + off;
     float ss = 0.0f;
@@ -156,13 +156,14 @@ __global__ void sigmoid_mul_kernel(T* __restrict__ o, const T* __restrict__ gate
 // (si == 1): a warp per j, lanes over i, a fixed tree.  A block per (token, head); the input row sits in shared memory.
 template <typename T, bool COLS>
 __global__ void head_product_kernel(const T* __restrict__ in, const T* __restrict__ W, T* __restrict__ out, int H, int I, int J,
-                                    long long sh, long long si, long long sj) {
+                                    long long sh, long long si, long long sj, int in_head, int out_head) {
+    // in_head, out_head: the distance between two heads of a row (a head's values may be part of a longer stretch)
     extern __shared__ float xin[];
     const int n = blockIdx.x, h = blockIdx.y;
-    for (int i = threadIdx.x; i < I; i += blockDim.x) xin[i] = mb_load(in + ((size_t)n * H + h) * I + i);
+    for (int i = threadIdx.x; i < I; i += blockDim.x) xin[i] = mb_load(in + ((size_t)n * H + h) * in_head + i);
     __syncthreads();
     const T* Wh = W + (size_t)h * sh;
-    T* o = out + ((size_t)n * H + h) * J;
+    T* o = out + ((size_t)n * H + h) * out_head;
     if (COLS) {
         for (int j = threadIdx.x; j < J; j += blockDim.x) {
             float acc = 0.0f;
@@ -218,14 +219,16 @@ static int post_norm_add_launch(float* x, const T* delta, const float* post_w, f
 template <typename T>
 static int rms_segments_launch(const T* in, int stride, int off_a, int wa, const float* w_a, T* out_a, int off_b, int wb,
                                const float* w_b, T* pool, const int* positions, const int* tok_row, const int* table,
-                               int max_blocks, int page, int num_pages, float eps, int N, int* err, cudaStream_t st) {
+                               int max_blocks, int page, int num_pages, float eps, int N, int* err, cudaStream_t st,
+                               int pool_row = 0) {
     if (N == 0) return 0;
-    if (wa < 0 || wb < 0 || (wb > 0 && (!pool || !table || page < 1))) return -2;
+    if (pool_row == 0) pool_row = wb;
+    if (wa < 0 || wb < 0 || pool_row < wb || (wb > 0 && (!pool || !table || page < 1))) return -2;
     const int W = wa > wb ? wa : wb;
     if (W == 0) return 0;
     rms_segments_kernel<T><<<dim3(N, wb > 0 ? 2 : 1), row_threads(W), 0, st>>>(in, stride, off_a, wa, w_a, out_a, off_b, wb,
                                                                               w_b, pool, positions, tok_row, table,
-                                                                              max_blocks, page, num_pages, eps, err);
+                                                                              max_blocks, page, num_pages, eps, err, pool_row);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -251,15 +254,18 @@ static int sigmoid_mul_launch(T* o, const T* gate, int gate_stride, int N, int C
 
 template <typename T>
 static int head_product_launch(const T* in, const T* W, T* out, int N, int H, int I, int J, long long sh, long long si,
-                               long long sj, cudaStream_t st) {
+                               long long sj, cudaStream_t st, int in_head = 0, int out_head = 0) {
     if (N == 0) return 0;
-    if (H < 1 || H > 65535 || I < 1 || J < 1 || I > 12000 || (sj != 1 && si != 1)) return -2;
+    if (in_head == 0) in_head = I;
+    if (out_head == 0) out_head = J;
+    if (H < 1 || H > 65535 || I < 1 || J < 1 || I > 12000 || (sj != 1 && si != 1) || in_head < I || out_head < J) return -2;
     const dim3 grid(N, H);
     if (sj == 1)
         head_product_kernel<T, true><<<grid, J >= 256 ? 256 : J >= 128 ? 128 : 64, (size_t)I * sizeof(float), st>>>(
-            in, W, out, H, I, J, sh, si, sj);
+            in, W, out, H, I, J, sh, si, sj, in_head, out_head);
     else
-        head_product_kernel<T, false><<<grid, 256, (size_t)I * sizeof(float), st>>>(in, W, out, H, I, J, sh, si, sj);
+        head_product_kernel<T, false><<<grid, 256, (size_t)I * sizeof(float), st>>>(in, W, out, H, I, J, sh, si, sj,
+                                                                                    in_head, out_head);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -282,6 +288,13 @@ static int head_product_launch(const T* in, const T* W, T* out, int N, int H, in
         return rms_segments_launch<T>((const T*)in, stride, off_a, wa, w_a, (T*)out_a, off_b, wb, w_b, (T*)pool,          \
                                       positions, tok_row, table, max_blocks, page, num_pages, eps, N, err, st);           \
     }                                                                                                                     \
+    MB_API int mb_rms_segments_wide_##SUF(const void* in, int stride, int off_a, int wa, const float* w_a, void* out_a,  \
+                                          int off_b, int wb, const float* w_b, void* pool, int pool_row,                  \
+                                          const int* positions, const int* tok_row, const int* table, int max_blocks,     \
+                                          int page, int num_pages, float eps, int N, int* err, cudaStream_t st) {         \
+        return rms_segments_launch<T>((const T*)in, stride, off_a, wa, w_a, (T*)out_a, off_b, wb, w_b, (T*)pool,          \
+                                      positions, tok_row, table, max_blocks, page, num_pages, eps, N, err, st, pool_row); \
+    }                                                                                                                     \
     MB_API int mb_gated_gather_##SUF(const void* z, const int* tokens, const void* table, int table_stride, int off,     \
                                      void* out, int N, int W, int V, int* err, cudaStream_t st) {                         \
         return gated_gather_launch<T>((const T*)z, tokens, (const T*)table, table_stride, off, (T*)out, N, W, V, err,     \
@@ -293,6 +306,11 @@ static int head_product_launch(const T* in, const T* W, T* out, int N, int H, in
     MB_API int mb_head_product_##SUF(const void* in, const void* W, void* out, int N, int H, int I, int J, long long sh,  \
                                      long long si, long long sj, cudaStream_t st) {                                       \
         return head_product_launch<T>((const T*)in, (const T*)W, (T*)out, N, H, I, J, sh, si, sj, st);                    \
+    }                                                                                                                     \
+    MB_API int mb_head_product_strided_##SUF(const void* in, int in_head, const void* W, void* out, int out_head, int N,  \
+                                             int H, int I, int J, long long sh, long long si, long long sj,               \
+                                             cudaStream_t st) {                                                           \
+        return head_product_launch<T>((const T*)in, (const T*)W, (T*)out, N, H, I, J, sh, si, sj, st, in_head, out_head); \
     }
 
 ROWWISE_API(f32, float)

@@ -310,6 +310,22 @@ def rms_segments(rows, off_a, w_a, out_a, off_b, w_b, pool, positions, tok_row, 
              _stream()), "rms_segments")
 
 
+def rms_segments_wide(rows, off_a, w_a, out_a, off_b, w_b, pool, positions, tok_row, table, page, num_pages, eps, err):
+    """rms_segments whose second stretch goes into the first len(w_b) values of a cache row that is wider than it: pool
+    (pages, 1, page, row)"""
+    _cuda(rows, w_a, out_a, w_b, pool, positions, tok_row, table)
+    N = rows.shape[0]
+    wa = 0 if w_a is None else w_a.shape[0]
+    wb = 0 if w_b is None else w_b.shape[0]
+    f = _fn("rowwise", "mb_rms_segments_wide_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_p(rows), rows.stride(0), off_a, wa, _p(w_a), _p(out_a), off_b, wb, _p(w_b), _p(pool),
+             pool.shape[-1] if pool is not None else 0, _p(positions), _p(tok_row), _p(table),
+             table.shape[1] if table is not None else 0, page, num_pages, float(eps), N, _p(err), _stream()),
+           "rms_segments_wide")
+
+
 def gated_gather(z, tokens, table, off, out, err):
     """out[n, j] = gelu_tanh(z[n, j]) * table[tokens[n], off + j]; z, out (N, W), table (V, any) in the activation dtype"""
     _cuda(z, tokens, table, out)
@@ -333,6 +349,26 @@ def sigmoid_mul(o, gate):
 # The per-head products run on the package's plain kernel up to this many tokens (and always in float32); larger bf16
 # steps hand them to the library's batched product.
 HEAD_PRODUCT = {"tokens": 32}
+
+
+def head_product_strided(x, I, w, out, J, heads, transposed):
+    """head_product on stretches of wider heads: x (N, heads * in_head) of whose every head the first I values are read,
+    out (N, heads * out_head) of whose every head the first J values are written; w as in head_product."""
+    _cuda(x, w, out)
+    N = x.shape[0]
+    in_head, out_head = x.shape[1] // heads, out.shape[1] // heads
+    if tuple(w.shape) != ((heads * I, J) if transposed else (heads * J, I)) or not w.is_contiguous():
+        raise KernelError("head_product: the matrix does not fit the heads")
+    if x.dtype == torch.bfloat16 and N > HEAD_PRODUCT["tokens"]:
+        a = x.view(N, heads, in_head)[:, :, :I].transpose(0, 1)
+        b = w.view(heads, I, J) if transposed else w.view(heads, J, I).transpose(1, 2)
+        out.view(N, heads, out_head)[:, :, :J].copy_(torch.bmm(a, b).transpose(0, 1))
+        return out
+    sh, si, sj = (I * J, J, 1) if transposed else (I * J, 1, I)
+    f = _fn("rowwise", "mb_head_product_strided_" + _suffix(x.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p])
+    _check(f(_p(x), in_head, _p(w), _p(out), out_head, N, heads, I, J, sh, si, sj, _stream()), "head_product")
+    return out
 
 
 def head_product(x, w, out, heads, transposed):
@@ -1374,3 +1410,129 @@ def read_logit_trace(pairs):
     import numpy as np
     a = np.ascontiguousarray(pairs.cpu().numpy() if hasattr(pairs, "cpu") else pairs, dtype=np.int32).reshape(-1, 2)
     return [(int(h), float(g)) for h, g in zip(a[:, 0].view(np.uint32), a[:, 1].copy().view(np.float32))]
+
+
+# ------------------------------------------------------------------------------------------------ layer norm on outputs
+def ln_add(x, y1, w, b, eps, copy=None, y2=None, s1=1.0, s2=1.0):
+    """x (N, D) float32 += layer_norm(s1 y1 + s2 y2) * w + b, row by row (y2 None: y1 alone); y1, y2 in the activation
+    dtype; copy: the new x in the activation dtype"""
+    _cuda(x, y1, y2, w, b, copy)
+    N, D = x.shape
+    f = _fn("layernorm", "mb_ln_add_" + _suffix(y1.dtype),
+            [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(y1), _p(y2), float(s1), float(s2), _p(w), _p(b), float(eps), _p(copy), N, D, _stream()), "ln_add")
+
+
+def layer_norm(x, rows, w, b, eps, out):
+    """out = layer_norm(x[rows]) * w + b (rows None: every row); x (N, D) float32, out in the activation dtype"""
+    _cuda(x, rows, w, b, out)
+    f = _fn("layernorm", "mb_layer_norm_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(rows), _p(w), _p(b), float(eps), _p(out), out.shape[0], x.shape[1], _stream()), "layer_norm")
+
+
+def to_rows(x, out):
+    """out = x (float32) in the activation dtype"""
+    _cuda(x, out)
+    f = _fn("layernorm", "mb_to_rows_" + _suffix(out.dtype), [c_void_p, c_void_p, c_ll, c_void_p])
+    _check(f(_p(x), _p(out), x.numel(), _stream()), "to_rows")
+
+
+def glu_clamped(gu, out, limit, alpha=1.702, shift=1.0):
+    """gu (N, 2F) = [gate | up] -> out (N, F) = g sigmoid(alpha g) (u + shift) with g = min(gate, limit),
+    u = clamp(up, -limit, limit); limit None: no clamps"""
+    _cuda(gu, out)
+    N, F = out.shape
+    f = _fn("elementwise", "mb_glu_clamped_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(f(_p(gu), _p(out), N, F, float(limit or 0.0), float(alpha), float(shift), _stream()), "glu_clamped")
+
+
+# ------------------------------------------------------------------------------------------------ gated recurrences
+def gla_gates(rows, z, zb, tau, q, k, v, g, H, dim, vdim):
+    """rows (N, >= 2 H dim + H vdim) = [q | k | v | ..] in the activation dtype, z (N, H dim) float32 decay logits, zb
+    their bias -> float32 q (times dim^-1/2), k (N, H dim), v (N, H vdim), g = sigmoid(z + zb)^(1 / tau)"""
+    _cuda(rows, z, zb, q, k, v, g)
+    f = _fn("gated_scan", "mb_gla_gates_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int] * 4 + [c_void_p])
+    _check(f(_p(rows), rows.stride(0), _p(z), _p(zb), 1.0 / float(tau), _p(q), _p(k), _p(v), _p(g), rows.shape[0], H, dim,
+             vdim, _stream()), "gla_gates")
+
+
+def ssd_gates(xbc, conv_bias, dt, dt_bias, A_log, q, k, v, g, H, G, P, NS):
+    """xbc (N, H P + 2 G NS) = [x | B | C] after the convolution (activation dtype), dt (N, H) float32 raw step sizes ->
+    float32 v = softplus(dt + dt_bias) silu(x + bias) (N, H P), k = silu(B + bias), q = silu(C + bias) (N, G NS),
+    g = exp(-exp(A_log) softplus(dt + dt_bias)) (N, H)"""
+    _cuda(xbc, conv_bias, dt, dt_bias, A_log, q, k, v, g)
+    f = _fn("gated_scan", "mb_ssd_gates_" + _suffix(xbc.dtype), [c_void_p] * 9 + [c_int] * 5 + [c_void_p])
+    _check(f(_p(xbc), _p(conv_bias), _p(dt), _p(dt_bias), _p(A_log), _p(q), _p(k), _p(v), _p(g), xbc.shape[0], H, G, P, NS,
+             _stream()), "ssd_gates")
+
+
+def ssd_out(o, xbc, conv_bias, D, z, w, out, H, P, parts, eps):
+    """out = rms over each of `parts` equal stretches of ((o + D x) silu(z)), times w: o (N, H P) float32 from the
+    recurrence, x = silu(xbc[:, :H P] + bias), z (N, H P) a view of the gate's logits, out in the activation dtype"""
+    _cuda(o, xbc, conv_bias, D, z, w, out)
+    f = _fn("gated_scan", "mb_ssd_out_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 4
+            + [c_float, c_void_p])
+    _check(f(_p(o), _p(xbc), xbc.stride(0), _p(conv_bias), _p(D), _p(z), z.stride(0), _p(w), _p(out), o.shape[0], H, P,
+             parts, float(eps), _stream()), "ssd_out")
+
+
+def gated_scan(q, k, v, g, o, state, seq, H, G, dim, vdim, per_head):
+    """S <- decay S + k v^T, o = S^T q per head and token, tokens of a sequence in order.  q, k (N, G dim), v (N, H vdim),
+    o (N, H vdim) float32; g (N, H dim) a decay per key channel, or (N, H) with per_head; state (slots, H dim vdim)
+    float32 (a view: slots state.stride(0) apart); seq = (q_start, q_len, state_slot) int32 device arrays"""
+    _cuda(q, k, v, g, o, state, *seq)
+    f = _fn("gated_scan", "mb_gated_scan", [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 6 + [c_void_p])
+    _check(f(_p(q), _p(k), _p(v), _p(g), _p(o), _p(state), state.stride(0), *[_p(t) for t in seq], seq[0].shape[0], H, G,
+             dim, vdim, 1 if per_head else 0, _stream()), "gated_scan")
+
+
+# ------------------------------------------------------------------------------------------------ normed, rotated heads
+def norm_rope_kv_write(rows, qw, kw, eps, freqs, RD, pairing, gain, positions, tok_row, table, kpool, vpool, H, KV, DK,
+                       DV, page, num_pages, err):
+    """rows (N, >= (H + KV) DK + KV DV) = [q | k | v | ..]: every q and k head divided by its root mean square and
+    multiplied by qw / kw (DK values; None: no norm), its first RD values rotated by the token's position (freqs (RD/2,)
+    float32 or None; pairing 0 adjacent, 1 halves; cos and sin times gain); q back in place, k and v into the pages:
+    kpool (pages, KV, page, DK), vpool (pages, KV, page, DV); both None: q only"""
+    _cuda(rows, qw, kw, freqs, positions, tok_row, table, kpool, vpool)
+    f = _fn("rotary_rows", "mb_norm_rope_kv_write_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_void_p])
+    _check(f(_p(rows), rows.stride(0), _p(qw), _p(kw), float(eps), _p(freqs), int(RD), int(pairing), float(gain),
+             _p(positions), _p(tok_row), _p(table), table.shape[1], _p(kpool), _p(vpool), rows.shape[0], H, KV, DK, DV, page,
+             num_pages, _p(err), _stream()), "norm_rope_kv_write")
+
+
+def latent_rope(q, q_head, q_off, qa, qa_head, qa_off, rows, kr_off, pool, pool_off, freqs, RD, W, pairing, gain,
+                positions, tok_row, table, H, page, num_pages, err):
+    """The strips of W values that latent attention rotates (the first RD of them turn): of every query head, q (N, H
+    q_head) at q_off, into qa (N, H qa_head) at qa_off; of the token's shared key strip, rows[:, kr_off:], into the
+    position's cache row at pool_off (pool (pages, 1, page, row); None: a layer that borrows its cache)"""
+    _cuda(q, qa, rows, pool, freqs, positions, tok_row, table)
+    f = _fn("rotary_rows", "mb_latent_rope_" + _suffix(q.dtype),
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+             c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p])
+    _check(f(_p(q), q.stride(0), q_head, q_off, _p(qa), qa_head, qa_off, _p(rows), rows.stride(0), kr_off, _p(pool),
+             pool.shape[-1] if pool is not None else 0, pool_off, _p(freqs), int(RD), int(W), int(pairing), float(gain),
+             _p(positions), _p(tok_row), _p(table), table.shape[1], q.shape[0], H, page, num_pages, _p(err), _stream()),
+           "latent_rope")
+
+
+def attention_general(q, q_stride, out, positions, tok_seq, table, kpool, vpool, H, KV, DK, DV, page, num_pages, window,
+                      scale, err, softcap=None, sinks=None, gate=None):
+    """The plain paged attention kernel in its general form: keys of DK and values of DV values (the pools' rows may be
+    wider: their last dimension is the distance between two positions), scores capped by softcap tanh(s / softcap), a
+    sink per query head in the denominator (sinks (H,) float32), the result of head h times sigmoid(gate[n, h])"""
+    _cuda(q, out, positions, tok_seq, table, kpool, vpool, sinks, gate)
+    N = out.shape[0]
+    f = _fn("attention_simple", "mb_attn_simple_ext_" + _suffix(out.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 10
+            + [c_float, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(q), q_stride, _p(out), _p(positions), _p(tok_seq), _p(table), table.shape[1], _p(kpool), _p(vpool), N, H,
+             KV, DK, DV, kpool.shape[-1], vpool.shape[-1], page, num_pages, window or 0, float(scale),
+             float(softcap or 0.0), _p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, _p(err), _stream()),
+           "attention_general")

@@ -37,6 +37,9 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "short_conv": ("short_conv.cu", []),
     "rowwise": ("rowwise.cu", []),                                     # learned positions, norms of sublayer outputs, latents
     "delta_rule": ("delta_rule.cu", []),                               # the gated delta rule and what feeds it
+    "gated_scan": ("gated_scan.cu", []),                               # gated linear attention, state-space duality
+    "layernorm": ("layernorm.cu", []),                                 # layer norm of sublayer outputs and of the stream
+    "rotary_rows": ("rotary_rows.cu", []),                             # head norms, rotation of strips, cache writes
     "moe": ("moe.cu", []),                                             # routed experts
     "stream": ("stream.cu", []),                                       # Dynamic Tanh, depth averaging, two normed outputs
     "retention": ("retention.cu", []),                                 # linear attention with a fixed decay per head
@@ -51,7 +54,8 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "sampling_noalloc": ("sampling_noalloc.cu", []),
     "trace": ("trace.cu", []),
 }
-EXTRA_SOURCES = {"sampling_noalloc": ["sampling.cu", "sampling_noalloc.h"]}      # files a library includes
+EXTRA_SOURCES = {"sampling_noalloc": ["sampling.cu", "sampling_noalloc.h"], "delta_rule": ["linear_scan.cuh"],
+                 "gated_scan": ["linear_scan.cuh"]}      # files a library includes
 _loaded = {}
 _lock = threading.Lock()
 

@@ -52,16 +52,27 @@ class PagedAttention:
     whoever keeps other things per position than keys and values of its own (one latent vector that is key and value at
     once, say) hands its pools in."""
 
-    def __init__(self, heads, kv_heads, head_dim, window=None, scale=None):
+    def __init__(self, heads, kv_heads, head_dim, window=None, scale=None, vdim=None, softcap=None, sinks=False,
+                 gated=False):
+        """vdim: the width of a value when it is not the key's (the result is heads * vdim wide); softcap: scores become
+        softcap tanh(s / softcap); sinks: attend() is handed one number per query head that joins the softmax's
+        denominator without a value; gated: attend() is handed a gate per token and query head (the head's result
+        times its sigmoid).  Any of the four, or pools whose rows are wider than what is read of them, make the
+        attention *general*: it runs on the kernels that take all of that."""
         self.H, self.KV, self.HD = int(heads), int(kv_heads), int(head_dim)
         if self.H % self.KV:
             raise ConfigError(f"{heads} heads do not divide into {kv_heads} kv heads")
         self.window = int(window) if window else None
         self.scale = float(scale) if scale else self.HD ** -0.5
+        self.VD = int(vdim) if vdim else self.HD
+        self.softcap = float(softcap) if softcap else None
+        self.general = self.VD != self.HD or self.softcap is not None or bool(sinks) or bool(gated)
 
     # ------------------------------------------------------------------------------------------ planning
     def uses_mma(self, ctx):
         import torch
+        if self.general:
+            return False
         return ctx.dtype == torch.bfloat16 and ctx.ops.attention_mma_supports(self.HD) and not ctx.options.get(
             "plain_attention", False)
 
@@ -176,14 +187,18 @@ class PagedAttention:
                              max_splits=max_splits, tc5=tc5, cluster=cluster)
 
     # ------------------------------------------------------------------------------------------ kernels
-    def attend(self, ctx, qkv, width, out, table, kpool, vpool, rope=None):
+    def attend(self, ctx, qkv, width, out, table, kpool, vpool, rope=None, sinks=None, gate=None):
         """The step's queries -- rows of qkv, `width` values apart, head h at column h * head_dim -- attend to the rows
-        of their sequences' pages; out (N, heads * head_dim).  rope = (bias, freqs, rotary dims, pairing): the decode
-        form of the TMA kernel rotates and stores the step's own keys and values from qkv itself."""
+        of their sequences' pages; out (N, heads * vdim).  rope = (bias, freqs, rotary dims, pairing): the decode
+        form of the TMA kernel rotates and stores the step's own keys and values from qkv itself.  sinks (heads,)
+        float32 and gate (a view (N, heads) of the gates' logits): see the constructor."""
         import torch
         ops = ctx.ops
         H, KV, HD = self.H, self.KV, self.HD
         page, pages = ctx.cache.page_size, ctx.cache.pool_pages
+        if self.general:
+            self.attend_general(ctx, qkv, width, out, table, kpool, vpool, sinks, gate)
+            return
         if self.uses_mma(ctx):
             plan = ctx.memo[self.plan_key()]
             nm = plan["name"]
@@ -221,6 +236,12 @@ class PagedAttention:
         else:
             ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
                                  HD, page, pages, self.window, self.scale, ctx.err)
+
+
+    def attend_general(self, ctx, q, width, out, table, kpool, vpool, sinks, gate):
+        ctx.ops.attention_general(q, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, self.H,
+                                  self.KV, self.HD, self.VD, ctx.cache.page_size, ctx.cache.pool_pages, self.window,
+                                  self.scale, ctx.err, self.softcap, sinks, gate)
 
 
 class Attention(PagedAttention):
@@ -327,3 +348,93 @@ class Attention(PagedAttention):
 
 
 register("mixer", "attention", Attention)
+
+
+class GatedAttention(PagedAttention):
+    """Grouped-query attention whose keys and values may differ in width, with, each optional: an RMS norm of every q
+    and k head before the rotation (`qk_norm`: weights `<q>.norm` and `<k>.norm` of head_dim values, shared by the
+    heads), a rotation of the first dims of a head (`position`, any rope spec), capped scores (`softcap`), a sink in
+    the softmax's denominator (`sink`: "unit" -- a sink of score zero, so one is added to the denominator -- or the name
+    of a tensor with one number per query head, or None) and a gate per token and query head (`gate`: head h's result
+    times sigmoid(Wg h)_h, Wg stored as `<g>`).  No biases.
+
+        q = Wq h (heads x dim), k = Wk h (kv_heads x dim), v = Wv h (kv_heads x vdim)
+        q, k <- rms(.) n per head;  rotated;  s = scale q . k, s <- cap tanh(s / cap)
+        p_j = e^s_j / (e^sink + sum_j e^s_j);  out = Wo concat_h(sigmoid(g_h) sum_j p_j v_j)
+
+    One product makes q, k, v and the gates' logits; one kernel norms, rotates and writes k and v to their pages; the
+    attention kernel takes cap, sink and gate in.  Norms, angles, scores and the softmax are float32."""
+
+    def __init__(self, hidden, heads, kv_heads, head_dim, vdim=None, scale=None, softcap=None, qk_norm=False, eps=1e-6,
+                 sink=None, gate=False, position=None, window=None, prefix="", names=None):
+        super().__init__(heads, kv_heads, head_dim, window, scale, vdim=vdim, softcap=softcap, sinks=sink is not None,
+                         gated=gate)
+        self.general = True         # this mixer's own path: separate key and value pools, q/k norms
+        self.D, self.eps, self.qk_norm, self.sink, self.gate = int(hidden), float(eps), bool(qk_norm), sink, bool(gate)
+        n = dict(q="q", k="k", v="v", g="g", o="o", q_norm="q.norm", k_norm="k.norm")
+        n.update(names or {})
+        self.n = {k: prefix + v for k, v in n.items()}
+        self.sink_name = prefix + sink if sink not in (None, "unit") else None
+        self.position = make("position", position) if isinstance(position, PartSpec) else position
+        self.w_in = self.wo = self.qw = self.kw = self.sinks = None
+
+    @property
+    def graph_safe(self):
+        return self.position is None or bool(getattr(self.position, "graph_safe", False))
+
+    def wants(self):
+        H, KV, HD, VD, D = self.H, self.KV, self.HD, self.VD, self.D
+        out = [Want(self.n["q"], (H * HD, D), "matrix"), Want(self.n["k"], (KV * HD, D), "matrix"),
+               Want(self.n["v"], (KV * VD, D), "matrix"), Want(self.n["o"], (D, H * VD), "matrix")]
+        if self.qk_norm:
+            out += [Want(self.n["q_norm"], (HD,), "vector"), Want(self.n["k_norm"], (HD,), "vector")]
+        if self.gate:
+            out.append(Want(self.n["g"], (H, D), "matrix"))
+        if self.sink_name:
+            out.append(Want(self.sink_name, (H,), "vector"))
+        return out + (self.position.wants() if self.position is not None else [])
+
+    def bind(self, tensors, env):
+        import torch
+        t = lambda k: tensors[self.n[k]]
+        self.w_in = torch.cat([t("q"), t("k"), t("v")] + ([t("g")] if self.gate else []), 0).contiguous()
+        self.wo = t("o")
+        self.qw, self.kw = (t("q_norm"), t("k_norm")) if self.qk_norm else (None, None)
+        if self.sink == "unit":
+            self.sinks = torch.zeros(self.H, dtype=torch.float32, device=env.device)
+        elif self.sink_name:
+            self.sinks = tensors[self.sink_name]
+        if self.position is not None:
+            self.position.bind(tensors, env)
+            if self.position.rotation() is None:
+                raise ConfigError("this attention rotates in its own kernel; its position part must hand it frequencies")
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window else "full", ((self.KV, self.HD), (self.KV, self.VD)), self.window)
+
+    def state_need(self):
+        return None
+
+    def forward(self, ctx, h, run, out="delta"):
+        ops, N = ctx.ops, ctx.N
+        H, KV, HD, VD = self.H, self.KV, self.HD, self.VD
+        rows = ctx.ws.get("gattn_in", N, (self.w_in.shape[0],), ctx.dtype)
+        ops.linear(h, self.w_in, out=rows)
+        group, kpool, vpool = ctx.cache.layer_cache(run.cache)
+        table, page, pages = group.device_table, ctx.cache.page_size, ctx.cache.pool_pages
+        freqs, rd, pairing, gain = None, 0, 0, 1.0
+        if self.position is not None:
+            freqs, rd, pairing = self.position.rotation()
+            gain = getattr(self.position, "gain", 1.0)
+        ops.norm_rope_kv_write(rows, self.qw, self.kw, self.eps, freqs, rd, pairing, gain, ctx.dev("positions"),
+                               ctx.dev("tok_row"), table, kpool if run.write else None, vpool if run.write else None, H, KV,
+                               HD, VD, page, pages, ctx.err)
+        o = ctx.ws.get("gattn_out", N, (H * VD,), ctx.dtype)
+        gate = rows[:, (H + KV) * HD + KV * VD:] if self.gate else None
+        self.attend(ctx, rows, rows.stride(0), o, table, kpool, vpool, sinks=self.sinks, gate=gate)
+        y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
+        ops.linear(o, self.wo, out=y)
+        return y, None
+
+
+register("mixer", "gated_attention", GatedAttention)

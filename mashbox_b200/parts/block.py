@@ -9,6 +9,8 @@ DepthAveragedBlock).
 
 "sandwich": a norm before AND after each sublayer, the normed output scaled per channel before it joins the stream,
 and optionally an input from the token itself at the layer's end (see SandwichBlock).
+
+"norm_after": the sublayers read the stream as it is and only their outputs are normed (see OutputNormBlock).
 """
 from ..errors import ConfigError
 from .base import make, register
@@ -290,3 +292,74 @@ class SandwichBlock:
 
 
 register("block", "sandwich", SandwichBlock)
+
+
+class OutputNormBlock:
+    """x += norm1(mixer(x));  x += norm2(ffn(x)): the sublayers read the stream itself, and what they return passes a
+    norm before it joins the stream.
+
+    The norm is any registered kind that offers `add_output` (norm, add into the float32 stream and the new stream in
+    the activation dtype, one kernel).  A mixer that is a weighted sum of two (`forward_parts`) hands both outputs and
+    their weights to that kernel instead of adding them itself.  `ffn` may be None.  Nothing is left pending; what the
+    block before left pending is added first."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, prefix, mixer, norm, ffn=None, names=None):
+        n = dict(norm1="norm1", norm2="norm2")
+        n.update(names or {})
+        self.norm1 = make("norm", norm, name=prefix + n["norm1"])
+        self.mixer = make("mixer", mixer, prefix=prefix)
+        self.ffn = make("feed_forward", ffn, prefix=prefix) if ffn is not None else None
+        self.norm2 = make("norm", norm, name=prefix + n["norm2"]) if self.ffn is not None else None
+        if not hasattr(self.norm1, "add_output"):
+            raise ConfigError("a block that norms its sublayers' outputs needs a norm kind with add_output")
+        self.width = self.norm1.width
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def prepare(self, ctx):
+        self.mixer.prepare(ctx)
+
+    def _stream(self, ctx, x, pending):
+        """-> the stream in the activation dtype (the float32 stream itself when that is the activation dtype)"""
+        import torch
+        if pending is not None:
+            delta, bias, *more = pending
+            ctx.memo.pop("held", None)
+            ctx.memo.pop("stream_rows", None)
+            for d in (delta, bias, *more):
+                if d is not None:
+                    x.add_(d)
+        if ctx.dtype == torch.float32:
+            return x, None
+        xa = ctx.ws.get("stream_rows", x.shape[0], (self.width,), ctx.dtype)
+        ready = ctx.memo.get("stream_rows")
+        if ready != x.data_ptr():
+            ctx.ops.to_rows(x, xa)
+            ctx.memo["stream_rows"] = x.data_ptr()
+        return xa, xa
+
+    def forward(self, ctx, x, pending, run):
+        ctx.after_norm = None
+        h, copy = self._stream(ctx, x, pending)
+        if hasattr(self.mixer, "forward_parts"):
+            a, sa, b, sb = self.mixer.forward_parts(ctx, h, run)
+            self.norm1.add_output(ctx, x, a, copy, b, sa, sb)
+        else:
+            y, bias = self.mixer.forward(ctx, h, run)
+            if bias is not None:
+                raise ConfigError("a block that norms its sublayers' outputs cannot defer a bias")
+            self.norm1.add_output(ctx, x, y, copy)
+        if self.ffn is not None:
+            y, bias = self.ffn.forward(ctx, h)
+            if bias is not None:
+                raise ConfigError("a block that norms its sublayers' outputs cannot defer a bias")
+            self.norm2.add_output(ctx, x, y, copy)
+        return None
+
+
+register("block", "norm_after", OutputNormBlock)

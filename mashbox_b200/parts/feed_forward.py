@@ -97,3 +97,41 @@ class DenseXielu:
 
 
 register("feed_forward", "dense_xielu", DenseXielu)
+
+
+class ClampedGLU:
+    """Wd (g sigmoid(alpha g) (u + shift)) with g = min(Wg h, limit) -- clamped from above only -- and
+    u = clamp(Wu h, -limit, limit): the routed experts' unit as a dense layer.  limit None: no clamps.  Gate and up weights
+    are concatenated at load so one product makes both; the activation is float32 arithmetic on the product's outputs."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, hidden, intermediate, limit=None, alpha=1.702, shift=1.0, prefix="", names=None):
+        self.D, self.F = int(hidden), int(intermediate)
+        self.limit = float(limit) if limit else None
+        self.alpha, self.shift = float(alpha), float(shift)
+        n = dict(gate="ffn_gate", up="ffn_up", down="ffn_down")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.wgu = self.wd = None
+
+    def wants(self):
+        return [Want(self.names["gate"], (self.F, self.D), "matrix"), Want(self.names["up"], (self.F, self.D), "matrix"),
+                Want(self.names["down"], (self.D, self.F), "matrix")]
+
+    def bind(self, tensors, env):
+        import torch
+        self.wgu = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], 0).contiguous()
+        self.wd = tensors[self.names["down"]]
+
+    def forward(self, ctx, h, out="delta"):
+        N = ctx.N
+        gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
+        ctx.ops.linear(h, self.wgu, out=gu)
+        a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
+        ctx.ops.glu_clamped(gu, a, self.limit, self.alpha, self.shift)
+        y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
+        ctx.ops.linear(a, self.wd, out=y)
+        return y, None
+
+
+register("feed_forward", "glu_clamped", ClampedGLU)

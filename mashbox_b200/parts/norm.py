@@ -103,3 +103,43 @@ class DynamicTanh:
 
 
 register("norm", "dyt", DynamicTanh)
+
+
+class LayerNorm:
+    """y = (v - mean(v)) / sqrt(var(v) + eps) * w + b over a row, var the mean of the squared deviations; w and b are
+    stored as `<name>` and `<name>.b`.  As a norm of the stream (`forward`) it is the model's last norm.  As a norm of a
+    sublayer's OUTPUT (`add_output`) one kernel norms what the sublayer returned (or a weighted sum of two such
+    outputs), adds it into the float32 stream and leaves the new stream in the activation dtype for the next reader."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, width, eps, name):
+        self.width, self.eps, self.name = int(width), float(eps), name
+        self.weight = self.bias = None
+
+    def wants(self):
+        return [Want(self.name, (self.width,), "vector"), Want(self.name + ".b", (self.width,), "vector")]
+
+    def bind(self, tensors, env):
+        self.weight, self.bias = tensors[self.name], tensors[self.name + ".b"]
+
+    def forward(self, ctx, x, pending=None, rows=None, out=None):
+        n_out = x.shape[0] if rows is None else rows.shape[0]
+        if out is None:
+            out = ctx.ws.get("normed" if rows is None else "normed_rows", n_out, (self.width,), ctx.dtype,
+                             reserve=None if rows is None else ctx.options.get("logit_rows", 8))
+        if pending is not None:
+            delta, bias, *more = pending
+            if bias is not None or more:
+                raise ConfigError("a layer norm of the stream takes one pending output without a bias")
+            ctx.memo.pop("held", None)
+            x.add_(delta)
+        ctx.ops.layer_norm(x, rows, self.weight, self.bias, self.eps, out)
+        return out
+
+    def add_output(self, ctx, x, y, copy=None, y2=None, s1=1.0, s2=1.0):
+        """x += ln(s1 y + s2 y2) w + b; copy: the new x in the activation dtype"""
+        ctx.memo.pop("held", None)
+        ctx.ops.ln_add(x, y, self.weight, self.bias, self.eps, copy, y2, s1, s2)
+
+
+register("norm", "layer", LayerNorm)

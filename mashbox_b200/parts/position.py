@@ -34,6 +34,20 @@ def llama3_factors(theta, dim, factor, low, high, original):
     return out
 
 
+def yarn_frequencies(theta, dim, factor, original, fast, slow):
+    """Frequencies bent between two wavelengths: pair i keeps f_i below `lo`, is slowed to f_i / factor above `hi`, and
+    blends linearly in between, where lo and hi are the (fractional) pair indexes whose wavelength makes `fast` and `slow`
+    turns over `original` positions: index(t) = dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(index(fast)),
+    0), hi = min(ceil(index(slow)), dim - 1).  Computed in float64, held in float32."""
+    def index(turns):
+        return dim * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+    lo, hi = max(math.floor(index(fast)), 0), min(math.ceil(index(slow)), dim - 1)
+    i = np.arange(dim // 2, dtype=np.float64)
+    f = float(theta) ** (-2.0 * i / dim)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32)
+
+
 def base_frequencies(theta, rotary_dim):
     return (1.0 / (np.float32(theta) ** (np.arange(0, rotary_dim, 2, dtype=np.int64).astype(np.float32)
                                          / np.float32(rotary_dim)))).astype(np.float32)
@@ -42,13 +56,18 @@ def base_frequencies(theta, rotary_dim):
 class RotaryEncoding:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, head_dim, rotary_dim, theta, scaling=None, pairing="adjacent", factors_name=None):
-        """scaling: None | ("linear", factor) | ("divide", factor) | ("llama3", factor, low, high, original); "linear"
-        multiplies every frequency by float32(1 / factor), "divide" divides it by the factor.  factors_name: canonical name
+        """scaling: None | ("linear", factor) | ("divide", factor) | ("llama3", factor, low, high, original) | ("yarn",
+        factor, original, fast, slow, gain coefficient); "linear" multiplies every frequency by float32(1 / factor),
+        "divide" divides it by the factor, "yarn" bends the frequencies (yarn_frequencies) and multiplies cos and sin by
+        `gain` = coefficient ln(factor) + 1 (whoever rotates reads `gain`; 1.0 for every other scaling).  factors_name: canonical name
         of an optional tensor of per-pair divisors that replaces the computed llama3 factors when the file has it."""
         self.head_dim, self.rotary_dim, self.theta = int(head_dim), int(rotary_dim), float(theta)
         self.scaling = tuple(scaling) if scaling else None
         self.pairing, self.factors_name = PAIRINGS[pairing], factors_name
         self.freqs = None
+        self.gain = 1.0
+        if self.scaling and self.scaling[0] == "yarn":
+            self.gain = float(self.scaling[5]) * math.log(float(self.scaling[1])) + 1.0
 
     def wants(self):
         if self.factors_name is None:
@@ -61,8 +80,11 @@ class RotaryEncoding:
         multiplies by 1/factor in the same expression, dense.py:316-317)."""
         f = base_frequencies(self.theta, self.rotary_dim)
         kind = self.scaling[0] if self.scaling else None
-        if kind not in (None, "linear", "divide", "llama3"):
+        if kind not in (None, "linear", "divide", "llama3", "yarn"):
             raise ValueError(self.scaling)
+        if kind == "yarn":
+            _, factor, original, fast, slow = self.scaling[:5]
+            return yarn_frequencies(self.theta, self.rotary_dim, float(factor), float(original), float(fast), float(slow))
         if stored_factors is not None:
             f = (f / np.asarray(stored_factors, np.float32)).astype(np.float32)
         elif kind == "llama3":
