@@ -1536,3 +1536,41 @@ def attention_general(q, q_stride, out, positions, tok_seq, table, kpool, vpool,
              KV, DK, DV, kpool.shape[-1], vpool.shape[-1], page, num_pages, window or 0, float(scale),
              float(softcap or 0.0), _p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, _p(err), _stream()),
            "attention_general")
+
+
+def attention_general_mma_supports(DK, DV):
+    """the tensor-core form of the general attention takes these key and value widths (bfloat16 only)"""
+    return DK % 16 == 0 and DV % 16 == 0 and 16 <= DK <= 256 and 16 <= DV <= 256
+
+
+def _general_mma_library(DK, DV):
+    from .build import variant
+    return variant(f"attention_general_mma_{DK}_{DV}", "attention_general_mma.cu", [f"-DGA_DK={DK}", f"-DGA_DV={DV}"])
+
+
+def attention_general_mma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
+                          table, part_o, part_ml, max_splits, H, KV, DK, DV, page, num_pages, window, scale, err,
+                          softcap=None, sinks=None, gate=None):
+    """attention_general on tensor cores (bfloat16): items are (sequence, row tile, split, splits) quadruples of the
+    prompt form (tiles of 64 packed rows) or, with decode, of the decode form (at most 16); split items leave partial
+    sums in part_o / part_ml for attention_general_merge.  Compiled for the pair (DK, DV) the first time it is asked for."""
+    _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, seq_row, table, part_o, part_ml, sinks, gate)
+    if out.dtype != torch.bfloat16 or not attention_general_mma_supports(DK, DV):
+        raise KernelError(f"attention_general_mma: no kernel for {out.dtype} with widths {DK} and {DV}")
+    f = _fn(_general_mma_library(DK, DV), "mb_attn_general_bf16",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int] + [c_void_p] * 6 + [c_int]
+            + [c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), kpool.shape[-1], vpool.shape[-1], _p(items), int(n_items),
+             1 if decode else 0, _p(q_start), _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1],
+             _p(part_o), _p(part_ml), max_splits, H, KV, DK, DV, page, num_pages, window or 0, float(scale),
+             float(softcap or 0.0), _p(sinks), _p(gate), gate.stride(0) if gate is not None else 0, _p(err), _stream()),
+           "attention_general_mma")
+
+
+def attention_general_merge(part_o, part_ml, part_tok, n_part, out, H, DK, DV, max_splits, sinks=None, gate=None):
+    """adds up the splits of the tokens whose keys were cut (part_tok: (token, splits) pairs), sink and gate included"""
+    _cuda(part_o, part_ml, part_tok, out, sinks, gate)
+    f = _fn(_general_mma_library(DK, DV), "mb_attn_general_merge_bf16",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_p(part_o), _p(part_ml), _p(part_tok), n_part, _p(out), H, DV, max_splits, _p(sinks), _p(gate),
+             gate.stride(0) if gate is not None else 0, _stream()), "attention_general_merge")

@@ -71,20 +71,26 @@ class PagedAttention:
     # ------------------------------------------------------------------------------------------ planning
     def uses_mma(self, ctx):
         import torch
-        if self.general:
-            return False
+        if self.general:        # keys and values of their own widths, caps, sinks, gates: the general tensor-core form
+            return (ctx.dtype == torch.bfloat16 and ctx.ops.attention_general_mma_supports(self.HD, self.VD)
+                    and not ctx.options.get("plain_attention", False))
         return ctx.dtype == torch.bfloat16 and ctx.ops.attention_mma_supports(self.HD) and not ctx.options.get(
             "plain_attention", False)
 
     def uses_tc5(self, ctx):
         """prompt-form tiles go to the tcgen05 kernel (its own number of packed rows per block, no splits) when it takes
         the sizes"""
-        return (ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
+        return (not self.general and ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
                 and ctx.ops.attention_tc5_supports(self.HD, ctx.cache.page_size))
+
+    def _tma(self, ctx):
+        """decode-form sequences go to the TMA kernel (whose splits may meet in a cluster)"""
+        return (not self.general and ctx.options.get("attention_kernel", "tma") == "tma"
+                and ctx.ops.attention_tma_supports(self.HD, ctx.cache.page_size))
 
     def plan_key(self):
         # everything the work list depends on: the head size decides the kernel and its rows per tile
-        return ("attention", self.H // self.KV, self.KV, self.HD, self.window)
+        return ("attention", self.H // self.KV, self.KV, self.HD, self.window, self.general)
 
     def prepare(self, ctx):
         """Work list of the flash kernel for this step: (sequence, row tile, split, splits) per block, decode-form
@@ -121,8 +127,7 @@ class PagedAttention:
         # launched as one thread-block cluster and their results meet in shared memory.
         cluster = 0
         page = ctx.cache.page_size
-        if (any(decode_form) and base[True] < target and ctx.options.get("attention_kernel", "tma") == "tma"
-                and ctx.ops.attention_tma_supports(self.HD, page) and ctx.options.get("attention_clusters", True)):
+        if (any(decode_form) and base[True] < target and self._tma(ctx) and ctx.options.get("attention_clusters", True)):
             raw = min(max_splits, -(-target // base[True]), max(key_tiles(s) for s in range(S) if decode_form[s]) // 2)
             want = 1 << (max(1, raw).bit_length() - 1)
             # only when the cluster holds all the splits the launch wants anyway: at one or two sequences (32 and 16
@@ -147,8 +152,7 @@ class PagedAttention:
         # the memory busy (8 kv heads, 8,192 keys: 20 sequences as 320 blocks take 8.2 ms a step, as 480 blocks 6.9; 40
         # as 320 blocks 12.4, as 1,280 10.6).  many_splits() picks the number of splits by a model of that.
         crowd = 0
-        if (not cluster and any(decode_form) and ctx.options.get("attention_kernel", "tma") == "tma"
-                and ctx.ops.attention_tma_supports(self.HD, page) and ctx.options.get("attention_splits") is None):
+        if (not cluster and any(decode_form) and self._tma(ctx) and ctx.options.get("attention_splits") is None):
             slots = 2 * ctx.ops.attention_tma_active_clusters(self.HD, 2)
             if slots and 2 * base[True] > slots:
                 work = sum(key_tiles(s) for s in range(S) if decode_form[s]) * KV
@@ -239,6 +243,28 @@ class PagedAttention:
 
 
     def attend_general(self, ctx, q, width, out, table, kpool, vpool, sinks, gate):
+        import torch
+        ops, H, KV = ctx.ops, self.H, self.KV
+        page, pages = ctx.cache.page_size, ctx.cache.pool_pages
+        if self.uses_mma(ctx) and width % 8 == 0 and kpool.shape[-1] % 8 == 0 and vpool.shape[-1] % 8 == 0:
+            plan = ctx.memo[self.plan_key()]
+            nm, n_part, ms = plan["name"], plan["n_part"], plan["max_splits"]
+            part_o = part_ml = None
+            if n_part:
+                part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (self.VD,), torch.float32, reserve=0)
+                part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
+            for form, n_items, decode in ((nm + "pre", plan["n_pre"], False), (nm + "mid", plan["n_mid"], False),
+                                          (nm + "dec", plan["n_dec"], True)):
+                if n_items:
+                    ops.attention_general_mma(q, width, out, kpool, vpool, ctx.dev(form), n_items, decode,
+                                              ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"),
+                                              ctx.dev(nm + "part_base"), ctx.dev("seq_row"), table, part_o, part_ml, ms, H,
+                                              KV, self.HD, self.VD, page, pages, self.window, self.scale, ctx.err,
+                                              self.softcap, sinks, gate)
+            if n_part:
+                ops.attention_general_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, self.HD, self.VD, ms,
+                                            sinks, gate)
+            return
         ctx.ops.attention_general(q, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, self.H,
                                   self.KV, self.HD, self.VD, ctx.cache.page_size, ctx.cache.pool_pages, self.window,
                                   self.scale, ctx.err, self.softcap, sinks, gate)
@@ -397,7 +423,11 @@ class GatedAttention(PagedAttention):
     def bind(self, tensors, env):
         import torch
         t = lambda k: tensors[self.n[k]]
-        self.w_in = torch.cat([t("q"), t("k"), t("v")] + ([t("g")] if self.gate else []), 0).contiguous()
+        parts = [t("q"), t("k"), t("v")] + ([t("g")] if self.gate else [])
+        rows = sum(p.shape[0] for p in parts)
+        if rows % 8:        # rows of the product start on 16-byte boundaries in bfloat16: zero rows behind the gates
+            parts.append(torch.zeros((8 - rows % 8, self.D), dtype=parts[0].dtype, device=parts[0].device))
+        self.w_in = torch.cat(parts, 0).contiguous()
         self.wo = t("o")
         self.qw, self.kw = (t("q_norm"), t("k_norm")) if self.qk_norm else (None, None)
         if self.sink == "unit":
@@ -430,7 +460,8 @@ class GatedAttention(PagedAttention):
                                ctx.dev("tok_row"), table, kpool if run.write else None, vpool if run.write else None, H, KV,
                                HD, VD, page, pages, ctx.err)
         o = ctx.ws.get("gattn_out", N, (H * VD,), ctx.dtype)
-        gate = rows[:, (H + KV) * HD + KV * VD:] if self.gate else None
+        off = (H + KV) * HD + KV * VD
+        gate = rows[:, off:off + H] if self.gate else None
         self.attend(ctx, rows, rows.stride(0), o, table, kpool, vpool, sinks=self.sinks, gate=gate)
         y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ops.linear(o, self.wo, out=y)
