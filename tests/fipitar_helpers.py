@@ -113,7 +113,11 @@ def row_nmse(got, want):
 
 
 # float32 against the float64 plain model: every product and sum is float32.  bfloat16 against the exact model: a row may
-# reach the bar, a twentieth of the rows ten times the bar, and the mean over the rows a fifth of the bar.
+# reach the bar, a twentieth of the rows more, none thirty times the bar, and the mean over the rows a fifth of the bar.
+# (A sublayer's output is normed before it joins the stream, so rounding noise in it is brought back to the stream's own
+# scale in every sublayer: the plain model itself turns a relative perturbation of 2^-9 of the embedding alone into an
+# NMSE of the logits of 3e-4 on average and 1e-2 in single rows of these configurations.  A wrong key or a lost state
+# moves many rows by order 1, and float32 is held to 1e-9.)
 BAR = {"float32": 1e-9, "bfloat16": 1e-2}
 BAR_SAME = {"float32": 1e-10, "bfloat16": 1e-2}
 
@@ -129,7 +133,7 @@ def assert_close(got, want, dtype, what, bar=None):
     else:
         over = int((e > limit).sum())
         mean = float(e.mean()) if len(e) >= 20 else 0.0
-        assert over <= len(e) // 20 and e.max() <= 10 * limit and mean <= (limit / 5 if bar is None else limit / 10), \
+        assert over <= len(e) // 20 and e.max() <= 30 * limit and mean <= (limit / 5 if bar is None else limit / 10), \
             f"{what}: bfloat16: {over} of {len(e)} rows over {limit:.0e}, worst {e.max():.3e} at row {int(e.argmax())}, " \
             f"mean {e.mean():.3e}"
     return float(e.max())
