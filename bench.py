@@ -725,6 +725,171 @@ def tosevik_configs(size, layers, vocab=32000, context=8192):
     return tv, sf
 
 
+# Layer sizes for `--design fipitar`: a layer of two mixers side by side first (attention with normed heads, capped scores
+# and a gate per head over keys of 128 and values of 64, beside a state-space recurrence with heads of 64 over a state of
+# 128), two layers of gated linear attention (heads of 128 x 128), a latent-attention layer last (latents of 128 with a
+# rotated strip of 64), a dense clamped feed-forward in every layer.  The Sufopel decoder beside it -- the closest design
+# the engine has: three recurrent layers with a matrix state per head and a decay per key channel, then a latent-attention
+# layer -- has the same width, layers, heads and head sizes and, here, a dense feed-forward of as many weights in every
+# layer and no token input.
+FIPITAR_SIZES = {
+    "1b": dict(width=2048, heads=16, dim=128, q_rank=768, kv_rank=128, rot=64, ff=8448),
+    "3b": dict(width=3072, heads=24, dim=128, q_rank=1024, kv_rank=128, rot=64, ff=9216),
+    "8b": dict(width=4096, heads=32, dim=128, q_rank=1536, kv_rank=128, rot=64, ff=16384),
+}
+
+
+def fipitar_configs(size, layers, vocab=32000, context=8192):
+    from mashbox_b200.config import fipitar as F
+    from mashbox_b200.config.sufopel import DeltaMixer, DenseFF, LatentMixer, SufopelConfig, SufopelLayer
+    z = FIPITAR_SIZES[size]
+    D, H, dim = z["width"], z["heads"], z["dim"]
+    left = F.AttentionMixer(heads=H, kv_heads=max(1, H // 4), dim=dim, vdim=dim // 2, scale=dim ** -0.5, softcap=30.0,
+                            rot=F.Rotation(dim // 2, 500000.0))
+    right = F.SsdMixer(heads=D // 64, vdim=64, state=128, groups=1, norm_groups=8, conv=4)
+    pair = F.PairMixer(left, right, 0.6, 1.1)
+    gla = F.GlaMixer(heads=H, dim=dim, vdim=dim, tau=16.0, a_rank=16)
+    lat = F.LatentMixer(heads=H, dim=dim, vdim=dim, q_rank=z["q_rank"], kv_rank=z["kv_rank"], scale=(dim + z["rot"]) ** -0.5,
+                        rot_dim=z["rot"], rot=F.Rotation(z["rot"], 250000.0, (2.0, 2048.0, 32.0, 1.0)))
+    kinds = (("parallel", pair), ("gla", gla), ("gla", gla), ("latent_attention", lat))
+    fp = F.FipitarConfig("Fipitar", width=D, vocab=vocab, norm_eps=1e-6, layers=tuple(
+        F.FipitarLayer(*kinds[i % 4], F.DenseFF(z["ff"], 7.0)) for i in range(layers)))
+    dl = DeltaMixer(heads=H, kv_heads=H, dim=dim, vdim=dim, conv=4, a_rank=16, g_rank=16)
+    la = LatentMixer(heads=H, dim=dim, vdim=dim, q_rank=z["q_rank"], kv_rank=z["kv_rank"], scale=dim ** -0.5)
+    sf = SufopelConfig("Sufopel", width=D, vocab=vocab, max_positions=context + 2048, embedding_scale=1.0, logit_scale=1.0,
+                       norm_eps=1e-6, side_dim=None, layers=tuple(
+        SufopelLayer("latent_attention" if i % 4 == 3 else "channel_delta", la if i % 4 == 3 else dl, DenseFF(z["ff"]))
+        for i in range(layers)))
+    return fp, sf
+
+
+def fipitar_kernels(a, z, P, B, ctx, pk):
+    """The kernels of the Fipitar decoder, each beside the like kernel of the Sufopel (or Llama) decoder at equal sizes:
+    CUDA-event time of single launches after an L2 flush, and the fraction of the measured peak that the algorithmic bytes
+    (copy bandwidth) or FLOPs (bf16 tensor throughput) come to."""
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.parts.attention import PagedAttention
+    dev = "cuda:0"
+    D, H, dim, R, rd, F, page = z["width"], z["heads"], z["dim"], z["kv_rank"], z["rot"], z["ff"], 16
+    KV, HS, PS, NS = max(1, H // 4), D // 64, 64, 128
+    gen = torch.Generator(device=dev).manual_seed(0)
+    bf = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    f32 = lambda *s: torch.randn(*s, generator=gen, device=dev) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = ops.new_error_word(dev)
+
+    def timed(f):
+        for _ in range(3):
+            f()
+        ts = []
+        for _ in range(max(5, a.steps // 4)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    mem = lambda us, nbytes: {"us": us, "gbs": nbytes / us / 1e3, "frac_of_copy_peak": nbytes / us / 1e3 / pk["hbm_gbs"]}
+    mat = lambda us, flops: {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / pk["bf16_tflops"]}
+    res = {}
+    # ---- the recurrences: a prompt of P tokens; B sequences of one token (state in, state out)
+    for form, N, S in (("prompt", P, 1), ("decode", B, B)):
+        seq = (i32([i * (N // S) for i in range(S)]), i32([N // S] * S), i32(list(range(S))))
+        q, k, v, o = f32(N, H * dim), f32(N, H * dim), f32(N, H * dim), f32(N, H * dim)
+        g, beta = torch.rand(N, H * dim, generator=gen, device=dev), torch.rand(N, H, generator=gen, device=dev)
+        state = torch.zeros(S, H * dim * dim, device=dev)
+        us = timed(lambda: ops.gated_scan(q, k, v, g, o, state, seq, H, H, dim, dim, False))
+        res[f"gla_scan_{form}"] = mem(us, 2 * S * H * dim * dim * 4 + N * H * dim * 5 * 4)
+        us = timed(lambda: ops.delta_rule(q, k, v, g, beta, o, state, seq, H, H, dim, dim))
+        res[f"delta_rule_sufopel_{form}"] = mem(us, 2 * S * H * dim * dim * 4 + N * H * dim * 5 * 4)
+        q, k, v, o = f32(N, NS), f32(N, NS), f32(N, HS * PS), f32(N, HS * PS)
+        g = torch.rand(N, HS, generator=gen, device=dev)
+        state = torch.zeros(S, HS * NS * PS, device=dev)
+        us = timed(lambda: ops.gated_scan(q, k, v, g, o, state, seq, HS, 1, NS, PS, True))
+        res[f"ssd_scan_{form}"] = mem(us, 2 * S * HS * NS * PS * 4 + N * (2 * NS + 2 * HS * PS + HS) * 4)
+    # ---- attention: P prompt tokens; B tokens over ctx keys.  The side-by-side layer's attention beside Llama's at equal
+    # heads and keys (its values are half as wide); latent attention with a rotated strip beside Sufopel's without one
+    left = PagedAttention(H, KV, dim, None, dim ** -0.5, vdim=dim // 2, softcap=30.0, sinks=True, gated=True)
+    llama = PagedAttention(H, KV, dim)
+    lat = PagedAttention(H, 1, R + rd, None, (dim + rd) ** -0.5, vdim=R, sinks=True)
+    lat.general = True
+    suf = PagedAttention(H, 1, R, None, dim ** -0.5)
+    sinks = f32(H)
+    for name, core, wk, wv, shared in (("attention_fipitar", left, dim, dim // 2, False), ("attention_llama", llama, dim, dim, False),
+                                       ("latent_attention_fipitar", lat, R + rd, R, True),
+                                       ("latent_attention_sufopel", suf, R, R, True)):
+        for form, N, S, klen in (("prompt", P, 1, P), ("decode", B, B, ctx)):
+            pages = S * -(-klen // page)
+            table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(S, -1)
+            kp = bf(pages, core.KV, page, wk)
+            vp = kp if shared else bf(pages, core.KV, page, wv)
+            q, o = bf(N, H * wk + 8 * ((H + 7) // 8)), torch.empty(N, H * wv, device=dev, dtype=torch.bfloat16)
+            q_len = [N // S] * S
+            ctx_ = _PlanContext(ops, dev, q_len, [klen - n for n in q_len], page, pages, err)
+            core.prepare(ctx_)
+            ctx_.inputs.upload()
+            extra = dict(sinks=sinks) if core.general else {}
+            if core is left:
+                extra["gate"] = q[:, H * wk:H * wk + H]
+            us = timed(lambda: core.attend(ctx_, q, q.stride(0), o, table, kp, vp, **extra))
+            nbytes = S * klen * core.KV * (wk + (0 if shared else wv)) * 2 + N * H * (wk + wv) * 2
+            if form == "prompt":
+                res[f"{name}_prompt"] = mat(us, 2 * H * (wk + wv) * P * P / 2)
+            else:
+                res[f"{name}_decode"] = mem(us, nbytes)
+    # ---- rows: what a sublayer's output passes on its way into the stream; the feed-forward's gate; heads before attention
+    for form, N in (("prompt", P), ("decode", B)):
+        x, y1, y2, w, b = f32(N, D), bf(N, D), bf(N, D), f32(D), f32(D)
+        nrm, cp = torch.empty(N, D, device=dev, dtype=torch.bfloat16), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.ln_add(x, y1, w, b, 1e-6, cp))
+        res[f"ln_add_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+        us = timed(lambda: ops.ln_add(x, y1, w, b, 1e-6, cp, y2, 0.6, 1.1))
+        res[f"ln_add_two_outputs_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2 + 2))
+        us = timed(lambda: ops.post_norm_add(x, y1, w, 1e-6, w, 1e-6, nrm))
+        res[f"post_norm_add_sufopel_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+        gu, act = bf(N, 2 * F), torch.empty(N, F, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.glu_clamped(gu, act, 7.0))
+        res[f"glu_clamped_{form}"] = mem(us, N * F * 6)
+        us = timed(lambda: ops.swiglu(gu, act))
+        res[f"swiglu_llama_{form}"] = mem(us, N * F * 6)
+        S = 1 if form == "prompt" else N
+        pages = S * -(-(N // S) // page) + 1
+        table = torch.arange(pages - 1, dtype=torch.int32, device=dev).reshape(S, -1)
+        positions, tok_row = i32([t % (N // S) for t in range(N)]), i32([t // (N // S) for t in range(N)])
+        rows = bf(N, (H + KV) * dim + KV * (dim // 2) + 8 * ((H + 7) // 8))
+        kp, vp = bf(pages, KV, page, dim), bf(pages, KV, page, dim // 2)
+        freqs, qw = f32(dim // 4).abs(), f32(dim)
+        us = timed(lambda: ops.norm_rope_kv_write(rows, qw, qw, 1e-6, freqs, dim // 2, 1, 1.0, positions, tok_row, table, kp, vp, H,
+                                                  KV, dim, dim // 2, page, pages, err))
+        res[f"norm_rope_kv_write_{form}"] = mem(us, N * ((H + KV) * dim * 2 + KV * (dim // 2)) * 2 + N * KV * dim * 2)
+        rows2, kp2, vp2 = bf(N, (H + 2 * KV) * dim), bf(pages, KV, page, dim), bf(pages, KV, page, dim)
+        us = timed(lambda: ops.rope_kv_write(rows2, None, positions, tok_row, table, kp2, vp2, freqs, H, KV, dim, dim // 2, 1, page,
+                                             pages, err))
+        res[f"rope_kv_write_llama_{form}"] = mem(us, N * ((H + KV) * dim * 2 + KV * dim) * 2 + N * 2 * KV * dim * 2)
+        # the gates of the recurrences and what follows them
+        grow, zz, zb = bf(N, 4 * H * dim), f32(N, H * dim), f32(H * dim)
+        q, k, v, g = (torch.empty(N, H * dim, device=dev) for _ in range(4))
+        us = timed(lambda: ops.gla_gates(grow, zz, zb, 16.0, q, k, v, g, H, dim, dim))
+        res[f"gla_gates_{form}"] = mem(us, N * H * dim * (3 * 2 + 4 + 4 * 4))
+        o, out = f32(N, H * dim), torch.empty(N, H * dim, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.gated_rms(o, grow[:, 3 * H * dim:], qw, out, H, dim, 1e-6, silu=True))
+        res[f"gated_rms_{form}"] = mem(us, N * H * dim * (4 + 2 + 2))
+        C = HS * PS + 2 * NS
+        xbc, cb, dt, hb = bf(N, C), f32(C), f32(N, HS), f32(HS)
+        q2, k2, v2, g2 = torch.empty(N, NS, device=dev), torch.empty(N, NS, device=dev), torch.empty(N, HS * PS, device=dev), torch.empty(N, HS, device=dev)
+        us = timed(lambda: ops.ssd_gates(xbc, cb, dt, hb, hb, q2, k2, v2, g2, HS, 1, PS, NS))
+        res[f"ssd_gates_{form}"] = mem(us, N * (C * 2 + HS * 4 + (2 * NS + HS * PS + HS) * 4))
+        o2, zg, wn, out2 = f32(N, HS * PS), bf(N, HS * PS), f32(HS * PS), torch.empty(N, HS * PS, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.ssd_out(o2, xbc, cb, hb, zg, wn, out2, HS, PS, 8, 1e-6))
+        res[f"ssd_out_{form}"] = mem(us, N * HS * PS * (4 + 2 + 2 + 2))
+    return res
+
+
 def run_design(a):
     """`--design luzosun --size 1b|3b|8b`: prefill and decode throughput of the Luzosun decoder and of the Llama decoder
     of equal size through the step function (random bf16 weights, `--layers` layers, default 4), and the kernels that
@@ -740,7 +905,11 @@ def run_design(a):
     layers = a.layers or 4
     design = a.design
     other = "llama"
-    if design == "tosevik":
+    if design == "fipitar":
+        z, other = FIPITAR_SIZES[a.size], "sufopel"
+        cfgs = dict(zip((design, other), fipitar_configs(a.size, layers, context=a.context)))
+        single_kernels = fipitar_kernels
+    elif design == "tosevik":
         z, other = TOSEVIK_SIZES[a.size], "sufopel"
         cfgs = dict(zip((design, other), tosevik_configs(a.size, layers, context=a.context)))
         single_kernels = tosevik_kernels
@@ -1288,8 +1457,8 @@ def main():
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
     ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--design", default="", choices=("", "luzosun", "sufopel", "tosevik"),
-                    help="another design beside the Llama decoder of equal size (tosevik: beside the Sufopel decoder): "
+    ap.add_argument("--design", default="", choices=("", "luzosun", "sufopel", "tosevik", "fipitar"),
+                    help="another design beside the Llama decoder of equal size (tosevik and fipitar: beside the Sufopel decoder): "
                     "prefill, decode, single kernels")
     ap.add_argument("--size", default="8b", choices=tuple(DESIGN_SIZES), help="--design: the layer sizes")
     ap.add_argument("--workload-warm", type=int, default=1, help="workloads: run the workload once untimed first")

@@ -188,7 +188,9 @@ __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
                 const int key = kb + nbase + j * 8 + 2 * tig + (e & 1);
                 const bool ok = key <= rpos[i] && key >= rlo[i];
                 float v = s[j][e] * GP.scale;
-                if (cap > 0.0f) v = cap * tanhf(v * inv_cap);
+                // tanh(x) = 1 - 2 / (e^2x + 1) on the fast exponential and division (a few ulp; both ends saturate cleanly):
+                // tanhf's own code was the longest chain of the tile (stalls on fixed-latency waits, tensor pipe 20 %)
+                if (cap > 0.0f) v = cap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
                 v = ok ? v * LOG2E : -INFINITY;
                 s[j][e] = v;
                 tmax[i] = fmaxf(tmax[i], v);

@@ -10,7 +10,7 @@
 // query head, the head's result times sigmoid(gate).
 #include "common.cuh"
 
-#define SIMPLE_MAX_HD 512          // the widest rows (two instantiations: up to 256, and up to this)
+#define SIMPLE_MAX_HD 1024         // the widest rows (three instantiations: up to 256, up to 512, and up to this)
 #define WARPS 4
 
 template <typename T, int MAXHD>
@@ -108,6 +108,10 @@ static int attn_simple_launch(const void* q, int q_stride, void* out, const int*
     const long long items = (long long)N * H;
     if (widest <= 256)
         attn_simple_kernel<T, 256><<<(unsigned)((items + WARPS - 1) / WARPS), WARPS * 32, 0, st>>>(
+            (const T*)q, q_stride, (T*)out, positions, tok_seq, table, max_blocks, (const T*)kpool, (const T*)vpool, N, H,
+            KV, HD, page, num_pages, window, scale, err, HDV, k_row, v_row, softcap, sinks, gate, gate_stride);
+    else if (widest <= 512)
+        attn_simple_kernel<T, 512><<<(unsigned)((items + WARPS - 1) / WARPS), WARPS * 32, 0, st>>>(
             (const T*)q, q_stride, (T*)out, positions, tok_seq, table, max_blocks, (const T*)kpool, (const T*)vpool, N, H,
             KV, HD, page, num_pages, window, scale, err, HDV, k_row, v_row, softcap, sinks, gate, gate_stride);
     else

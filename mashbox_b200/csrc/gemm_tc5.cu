@@ -270,6 +270,11 @@ MB_API int mb_gemm_tc5_grouped_gated_bf16(const void* act, const void* W, void* 
     if (!tile_expert) return -2;
     return tc5_launch<4>(act, W, out, N, M, K, err, st, limit, alpha, tile_expert, experts, shift);
 }
+// The same gate as a dense layer's: W (2 M, K) = [gate rows | up rows], any N; limit <= 0: no clamps.
+MB_API int mb_gemm_tc5_glu_clamped_bf16(const void* act, const void* W, void* out, int N, int M, int K, float limit,
+                                        float alpha, float shift, int* err, cudaStream_t st) {
+    return tc5_launch<4>(act, W, out, N, M, K, err, st, limit > 0.0f ? limit : 3.0e38f, alpha, nullptr, 1, shift);
+}
 // W (experts, M, K); out (N, M) float32
 MB_API int mb_gemm_tc5_grouped_f32out(const void* act, const void* W, void* out, int N, int M, int K, const int* tile_expert,
                                       int experts, int* err, cudaStream_t st) {

@@ -30,44 +30,71 @@ __device__ __forceinline__ void rr_rotate(float* v, int RD, int pairing, const f
     }
 }
 
+// grid (N, ceil((H + KV) / NR_WARPS)): a block takes NR_WARPS of a token's H + KV heads, a warp a head; the token's cosines
+// and sines are made once per block, by all its threads.  Shared memory: RD floats of cos and sin, then DK floats per warp.
+#define NR_WARPS 8
 template <typename T>
-__global__ void norm_rope_kv_write_kernel(T* __restrict__ rows, int stride, const float* __restrict__ qw,
-                                          const float* __restrict__ kw, float eps, const float* __restrict__ freqs, int RD,
-                                          int pairing, float gain, const int* __restrict__ positions,
-                                          const int* __restrict__ tok_row, const int* __restrict__ table, int max_blocks,
-                                          T* __restrict__ kpool, T* __restrict__ vpool, int H, int KV, int DK, int DV,
-                                          int page, int num_pages, int* err) {
-    extern __shared__ float vals[];
-    __shared__ float scratch[32];
-    const int n = blockIdx.x, b = blockIdx.y;
-    const bool is_q = b < H;
-    const int kvh = b - H;
-    T* src = rows + (size_t)n * stride + (is_q ? (size_t)b * DK : (size_t)H * DK + (size_t)kvh * DK);
+__global__ void __launch_bounds__(NR_WARPS * 32) norm_rope_kv_write_kernel(
+    T* __restrict__ rows, int stride, const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+    const float* __restrict__ freqs, int RD, int pairing, float gain, const int* __restrict__ positions,
+    const int* __restrict__ tok_row, const int* __restrict__ table, int max_blocks, T* __restrict__ kpool,
+    T* __restrict__ vpool, int H, int KV, int DK, int DV, int page, int num_pages, int* err) {
+    extern __shared__ float smem[];
+    float* cs = smem;                       // cos of the RD / 2 pairs, then sin
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, half = RD / 2;
+    float* vals = smem + RD + warp * DK;
     const int pos = positions[n];
-    const float* w = is_q ? qw : kw;
-    float ss = 0.0f;
-    for (int d = threadIdx.x; d < DK; d += blockDim.x) { const float x = mb_load(src + d); vals[d] = x; ss = fmaf(x, x, ss); }
-    if (w) {
-        const float r = 1.0f / sqrtf(mb_block_sum(ss, scratch) / (float)DK + eps);
-        for (int d = threadIdx.x; d < DK; d += blockDim.x) vals[d] = vals[d] * r * w[d];
+    if (freqs) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, c;
+            sincosf((float)pos * freqs[i], &sn, &c);
+            cs[i] = c * gain;
+            cs[half + i] = sn * gain;
+        }
     }
     __syncthreads();
-    if (freqs && RD > 0) rr_rotate(vals, RD, pairing, freqs, (float)pos, gain);
-    __syncthreads();
-    if (is_q) {
-        for (int d = threadIdx.x; d < DK; d += blockDim.x) mb_store(src + d, vals[d]);
-        return;
+    size_t slot = 0;
+    bool have_page = false;
+    if (kpool) {
+        const int pg = table[(size_t)tok_row[n] * max_blocks + pos / page];
+        if (pg < 0 || pg >= num_pages) {
+            if (threadIdx.x == 0) mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+        } else {
+            have_page = true;
+            slot = (size_t)pg * KV * page + (pos % page);           // + kv head * page
+        }
     }
-    if (!kpool) return;
-    const int pg = table[(size_t)tok_row[n] * max_blocks + pos / page];
-    if (pg < 0 || pg >= num_pages) {
-        if (threadIdx.x == 0) mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
-        return;
+    for (int b = blockIdx.y * NR_WARPS + warp; b < H + KV; b += gridDim.y * NR_WARPS) {
+        const bool is_q = b < H;
+        const int kvh = b - H;
+        T* src = rows + (size_t)n * stride + (size_t)b * DK;       // the k heads follow the q heads
+        const float* w = is_q ? qw : kw;
+        float ss = 0.0f;
+        for (int d = lane; d < DK; d += 32) { const float x = mb_load(src + d); vals[d] = x; ss = fmaf(x, x, ss); }
+        if (w) {
+            const float r = 1.0f / sqrtf(mb_warp_sum(ss) / (float)DK + eps);
+            for (int d = lane; d < DK; d += 32) vals[d] = vals[d] * r * w[d];
+        }
+        __syncwarp();
+        if (freqs) {
+            for (int i = lane; i < half; i += 32) {
+                const int a = pairing ? i : 2 * i, c = pairing ? i + half : 2 * i + 1;
+                const float u = vals[a], v = vals[c];
+                vals[a] = u * cs[i] - v * cs[half + i];
+                vals[c] = v * cs[i] + u * cs[half + i];
+            }
+        }
+        __syncwarp();
+        if (is_q) {
+            for (int d = lane; d < DK; d += 32) mb_store(src + d, vals[d]);
+        } else if (have_page) {
+            const size_t row = slot + (size_t)kvh * page;
+            for (int d = lane; d < DK; d += 32) mb_store(kpool + row * DK + d, vals[d]);
+            const T* vs = rows + (size_t)n * stride + (size_t)(H + KV) * DK + (size_t)kvh * DV;
+            for (int d = lane; d < DV; d += 32) vpool[row * DV + d] = vs[d];
+        }
+        __syncwarp();
     }
-    const size_t slot = ((size_t)pg * KV + kvh) * page + (pos % page);
-    for (int d = threadIdx.x; d < DK; d += blockDim.x) mb_store(kpool + slot * DK + d, vals[d]);
-    const T* vs = rows + (size_t)n * stride + (size_t)(H + KV) * DK + (size_t)kvh * DV;
-    for (int d = threadIdx.x; d < DV; d += blockDim.x) vpool[slot * DV + d] = vs[d];
 }
 
 template <typename T>
@@ -107,10 +134,11 @@ __global__ void latent_rope_kernel(const T* __restrict__ q, int q_stride, int q_
                                            int N, int H, int KV, int DK, int DV, int page, int num_pages, int* err,       \
                                            cudaStream_t st) {                                                             \
         if (N == 0) return 0;                                                                                              \
-        if (H < 1 || KV < 1 || H + KV > 65535 || DK < 1 || DV < 1 || DK > 8192 || RD < 0 || RD > DK || (RD & 1) ||          \
+        if (H < 1 || KV < 1 || H + KV > 65535 * NR_WARPS || DK < 1 || DV < 1 || DK > 1024 || RD < 0 || RD > DK || (RD & 1) ||                            \
             page < 1)                                                                                                      \
             return -2;                                                                                                     \
-        norm_rope_kv_write_kernel<T><<<dim3(N, H + KV), DK > 64 ? 128 : 64, (size_t)DK * sizeof(float), st>>>(             \
+        norm_rope_kv_write_kernel<T><<<dim3(N, (H + KV + NR_WARPS - 1) / NR_WARPS), NR_WARPS * 32,                        \
+                                       (size_t)(RD + NR_WARPS * DK) * sizeof(float), st>>>(                               \
             (T*)rows, stride, qw, kw, eps, freqs, RD, pairing, gain, positions, tok_row, table, max_blocks, (T*)kpool,     \
             (T*)vpool, H, KV, DK, DV, page, num_pages, err);                                                               \
         MB_LAUNCH_CHECK();                                                                                                 \

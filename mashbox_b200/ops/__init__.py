@@ -1053,6 +1053,21 @@ def linear_xielu(a, w, out, ap, an):
     return out
 
 
+def linear_glu_clamped(a, wgu, out, limit, alpha=1.702, shift=1.0):
+    """a (N, K) bf16, wgu (2F, K) = [gate rows | up rows] -> out (N, F) = g sigmoid(alpha g) (u + shift) with the clamps of
+    glu_clamped, one kernel (the tcgen05 product with the gate in its epilogue); shapes fused_xielu_supports() takes"""
+    _cuda(a, wgu, out)
+    N, K = a.shape
+    if not (tc5_supports(N, out.shape[1], K, "swiglu") and a.dtype == torch.bfloat16 and a.is_contiguous()
+            and wgu.is_contiguous() and out.is_contiguous()):
+        raise KernelError("linear_glu_clamped: no fused kernel takes these sizes")
+    f = _fn("gemm_tc5", "mb_gemm_tc5_glu_clamped_bf16", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                                                         c_float, c_void_p, c_void_p])
+    _check(f(_p(a), _p(wgu), _p(out), N, out.shape[1], K, float(limit or 0.0), float(alpha), float(shift),
+             _p(error_word(a.device)), _stream()), "gemm_tc5_glu_clamped")
+    return out
+
+
 def linear_swiglu(a, wgu, out):
     """a (N, K) bf16, wgu (2F, K) = [gate rows | up rows] -> out (N, F) = silu(a Wg^T) * (a Wu^T), one kernel: the
     tcgen05 product for prompt portions, the matrix-vector or the weight-streaming kernel for decode batches (where enabled).
@@ -1485,9 +1500,11 @@ def gated_scan(q, k, v, g, o, state, seq, H, G, dim, vdim, per_head):
     o (N, H vdim) float32; g (N, H dim) a decay per key channel, or (N, H) with per_head; state (slots, H dim vdim)
     float32 (a view: slots state.stride(0) apart); seq = (q_start, q_len, state_slot) int32 device arrays"""
     _cuda(q, k, v, g, o, state, *seq)
-    f = _fn("gated_scan", "mb_gated_scan", [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 6 + [c_void_p])
-    _check(f(_p(q), _p(k), _p(v), _p(g), _p(o), _p(state), state.stride(0), *[_p(t) for t in seq], seq[0].shape[0], H, G,
-             dim, vdim, 1 if per_head else 0, _stream()), "gated_scan")
+    f = _fn("gated_scan", "mb_gated_scan", [c_void_p] * 6 + [c_ll] + [c_void_p] * 3 + [c_int] * 7 + [c_void_p])
+    S = seq[0].shape[0]
+    # which layout of the state over threads: by the step's tokens per sequence (from the lengths of the arrays alone)
+    _check(f(_p(q), _p(k), _p(v), _p(g), _p(o), _p(state), state.stride(0), *[_p(t) for t in seq], S, H, G,
+             dim, vdim, 1 if per_head else 0, 1 if q.shape[0] > 4 * S else 0, _stream()), "gated_scan")
 
 
 # ------------------------------------------------------------------------------------------------ normed, rotated heads

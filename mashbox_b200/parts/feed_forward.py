@@ -124,11 +124,15 @@ class ClampedGLU:
         self.wd = tensors[self.names["down"]]
 
     def forward(self, ctx, h, out="delta"):
+        import torch
         N = ctx.N
-        gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
-        ctx.ops.linear(h, self.wgu, out=gu)
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
-        ctx.ops.glu_clamped(gu, a, self.limit, self.alpha, self.shift)
+        if ctx.dtype == torch.bfloat16 and ctx.ops.fused_xielu_supports(N, self.F, self.D) and h.is_contiguous():
+            ctx.ops.linear_glu_clamped(h, self.wgu, a, self.limit, self.alpha, self.shift)      # the gate in the product's epilogue
+        else:
+            gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
+            ctx.ops.linear(h, self.wgu, out=gu)
+            ctx.ops.glu_clamped(gu, a, self.limit, self.alpha, self.shift)
         y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)
         return y, None
