@@ -71,7 +71,9 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* pool, int row_e
     }
 }
 
-template <int DK, int DV, bool DECODE, int STAGES>
+// SHARED: keys and values are one pool (a position's row is its key, the value that row's first DV values): the value
+// product reads the key tile, nothing is fetched twice and a stage is a third to a half smaller.
+template <int DK, int DV, bool DECODE, int STAGES, bool SHARED>
 __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
     const AttnParams& P = GP.a;
     constexpr int BM = DECODE ? 16 : 64, BN = 64, CHQ = DK / 8;
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
     constexpr int KS = DK / 16;             // k steps of q k^T
     constexpr int DT = DV / 8;              // 8-wide tiles of the output
     constexpr int ROWK = tile_row<DK>(), ROWV = tile_row<DV>();     // elements of a tile's row in shared memory
-    constexpr int STAGE = BN * (ROWK + ROWV);                       // a stage: the key tile, then the value tile
+    constexpr int STAGE = BN * (ROWK + (SHARED ? 0 : ROWV));        // a stage: the key tile, then the value tile
     constexpr bool QREG = DK <= 128;        // the query fragments stay in registers (above: read again for every key tile)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
     auto fetch = [&](int t) {
         bf16* st = kvs + (size_t)((t - t_begin) % STAGES) * STAGE;
         load_tile<DK, BN>(st, P.kpool, GP.k_row, P, tb, kvh, lo_al + t * BN, lo, hi, tid);
-        load_tile<DV, BN>(st + BN * ROWK, P.vpool, GP.v_row, P, tb, kvh, lo_al + t * BN, lo, hi, tid);
+        if (!SHARED) load_tile<DV, BN>(st + BN * ROWK, P.vpool, GP.v_row, P, tb, kvh, lo_al + t * BN, lo, hi, tid);
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
             cp_async_commit();
         }
         const bf16* kt = kvs + (size_t)((t - t_begin) % STAGES) * STAGE;
-        const bf16* vt = kt + BN * ROWK;
+        const bf16* vt = SHARED ? kt : kt + BN * ROWK;
         const int kb = lo_al + t * BN;
 
         float s[NT][4];
@@ -228,7 +230,8 @@ __global__ void __launch_bounds__(128) attn_general_kernel(const GenParams GP) {
 #pragma unroll
             for (int dp = 0; dp < DV / 16; dp++) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, vt + swz<DV>(nbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
+                const int vrow = nbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, vc = dp * 2 + (lane >> 4);
+                ldmatrix_x4_trans(b, vt + (SHARED ? swz<DK>(vrow, vc) : swz<DV>(vrow, vc)));
                 mma_bf16(o[2 * dp], a, b[0], b[1]);
                 mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
             }
@@ -331,21 +334,21 @@ __global__ void attn_general_merge_kernel(const GenParams GP, const int2* __rest
     }
 }
 
-template <int DK, int DV, bool DECODE, int STAGES>
+template <int DK, int DV, bool DECODE, int STAGES, bool SHARED>
 static int launch_general(const GenParams& P, int n_items, cudaStream_t st) {
     constexpr int BM = DECODE ? 16 : 64;
-    constexpr int ROWK = tile_row<DK>(), ROWV = tile_row<DV>();
+    constexpr int ROWK = tile_row<DK>(), ROWV = SHARED ? 0 : tile_row<DV>();
     size_t smem = (size_t)BM * ROWK * 2 + (size_t)STAGES * 64 * (ROWK + ROWV) * 2;
     const size_t merge = (size_t)(4 * 16 * DV + 2 * 4 * 16) * 4 + (size_t)BM * ROWK * 2;
     if (DECODE && merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_general_kernel<DK, DV, DECODE, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(attn_general_kernel<DK, DV, DECODE, STAGES, SHARED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_general_kernel<DK, DV, DECODE, STAGES><<<dim3(n_items, P.a.KV), 128, smem, st>>>(P);
+    attn_general_kernel<DK, DV, DECODE, STAGES, SHARED><<<dim3(n_items, P.a.KV), 128, smem, st>>>(P);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -393,8 +396,12 @@ MB_API int mb_attn_general_bf16(const void* q, int q_stride, void* out, const vo
             part_o, part_ml, max_splits, H, KV, page, num_pages, window, scale, softcap, sinks, gate, gate_stride, err);
     GP.a.items = (const int4*)items;
     constexpr int WIDE = (GA_DK > 128 || GA_DV > 128) ? 1 : 0;
-    return decode ? launch_general<GA_DK, GA_DV, true, (WIDE ? 2 : 3)>(GP, n_items, st)
-                  : launch_general<GA_DK, GA_DV, false, 2>(GP, n_items, st);
+    constexpr bool CAN_SHARE = GA_DV <= GA_DK;
+    if (CAN_SHARE && kpool == vpool && k_row == v_row)
+        return decode ? launch_general<GA_DK, GA_DV, true, 3, CAN_SHARE>(GP, n_items, st)
+                      : launch_general<GA_DK, GA_DV, false, 2, CAN_SHARE>(GP, n_items, st);
+    return decode ? launch_general<GA_DK, GA_DV, true, (WIDE ? 2 : 3), false>(GP, n_items, st)
+                  : launch_general<GA_DK, GA_DV, false, 2, false>(GP, n_items, st);
 }
 
 MB_API int mb_attn_general_merge_bf16(float* part_o, float* part_ml, const void* part_tok, int n_part, void* out, int H,
