@@ -112,14 +112,19 @@ def row_nmse(got, want):
     return ((got - want) ** 2).sum(-1) / np.maximum((want ** 2).sum(-1), 1e-300)
 
 
-# float32 against the float64 plain model: every product and sum is float32.  bfloat16 against the exact model: a row may
-# reach the bar, a twentieth of the rows more, none thirty times the bar, and the mean over the rows a fifth of the bar.
-# (A sublayer's output is normed before it joins the stream, so rounding noise in it is brought back to the stream's own
-# scale in every sublayer: the plain model itself turns a relative perturbation of 2^-9 of the embedding alone into an
-# NMSE of the logits of 3e-4 on average and 1e-2 in single rows of these configurations.  A wrong key or a lost state
-# moves many rows by order 1, and float32 is held to 1e-9.)
-# The float32 bar follows from the same measurement: the worst row multiplies a perturbation's variance by 2,400, and a
-# float32 implementation rounds (6e-8 relative) some dozens of times on the way: 1e-13 x 2,400 x 10 is 2e-9.
+# float32 against the float64 plain model: every product and sum is float32; the bar follows from a measurement: a
+# sublayer's output is normed before it joins the stream, so rounding noise is brought back to the stream's own scale in
+# every sublayer; the plain model itself multiplies the variance of a small perturbation of its embedding by up to 2,400
+# on the way to the logits, and a float32 implementation rounds (6e-8 relative) some dozens of times: 1e-13 x 2,400 x 10
+# is 2e-9.
+# bfloat16 against the exact model: half of the rows under a twentieth of the bar, nine in ten under the bar, no more than
+# a twentieth of the rows over it, and the mean of all but that twentieth under a fifth of it; the worst rows themselves
+# are not bounded.  With random weights a recurrence's output (a sum over the state that is a hundred times a single
+# term) cancels at some token to a twentieth of its usual size, and the norm after it brings what is left -- rounding noise
+# included -- back to full scale: at such a row two CORRECT bfloat16 implementations (the plain attention kernel and the
+# tensor-core one, which differ by an ulp here and there two layers earlier) were measured 0.4 apart in NMSE, each
+# matching a float64 scan of its own inputs to 1e-5.  A wrong key, a window one token off or a lost state moves most rows
+# after it by order 1, which the median and the tenth-worst row catch; exactness is float32's to show.
 BAR = {"float32": 1e-8, "bfloat16": 1e-2}
 BAR_SAME = {"float32": 1e-9, "bfloat16": 1e-2}
 
@@ -134,8 +139,13 @@ def assert_close(got, want, dtype, what, bar=None):
         assert e.max() <= limit, f"{what}: float32 NMSE {e.max():.3e} at row {int(e.argmax())}"
     else:
         over = int((e > limit).sum())
-        mean = float(e.mean()) if len(e) >= 20 else 0.0
-        assert over <= len(e) // 20 and e.max() <= 30 * limit and mean <= (limit / 5 if bar is None else limit / 10), \
-            f"{what}: bfloat16: {over} of {len(e)} rows over {limit:.0e}, worst {e.max():.3e} at row {int(e.argmax())}, " \
-            f"mean {e.mean():.3e}"
+        srt = np.sort(e)
+        kept = srt[:len(e) - len(e) // 20] if len(e) >= 20 else srt[:0]
+        mean = float(kept.mean()) if len(kept) else 0.0
+        p90 = float(srt[(len(e) * 9) // 10]) if len(e) >= 20 else 0.0
+        ok = over <= max(len(e) // 20, 0) and float(np.median(e)) <= limit / 20 and p90 <= limit and mean <= limit / 5
+        if len(e) < 20:                     # a few rows: each under the bar
+            ok = float(e.max()) <= limit
+        assert ok, f"{what}: bfloat16: {over} of {len(e)} rows over {limit:.0e}, worst {e.max():.3e} at row " \
+                   f"{int(e.argmax())}, median {np.median(e):.3e}, ninth decile {p90:.3e}, mean without the worst twentieth {mean:.3e}"
     return float(e.max())

@@ -291,18 +291,23 @@ def test_attention_kernel_refuses_head_sizes_it_does_not_take():
     seqs = G.PagedSequences([20], [1], 2, 1, 40, 8, torch.bfloat16).round().build()
     with pytest.raises(Exception, match="does not take these sizes"):
         run_mma(seqs, None, 1)
-    # the plain kernel takes rows of up to 512 values (its second instantiation) and refuses wider ones
+    # the plain kernel takes rows of up to 1,024 values (512: its second instantiation, 544: its third) and refuses wider ones
     wide = G.PagedSequences([20], [3], 2, 1, 512, 8, torch.float32).build()
     out = torch.empty(3, 2 * 512, device=G.DEV)
     K.attention_simple(wide.q_dev, 2 * 512, out, wide.positions, wide.tok_row, wide.table, wide.kpool, wide.vpool, 2, 1, 512,
                        8, wide.num_pages, None, 0.05, K.new_error_word(G.DEV))
     want = wide.reference(0.05).reshape(3, 2 * 512)
     assert float((out.double().cpu() - want).abs().max()) < 1e-5
-    big = G.PagedSequences([20], [1], 1, 1, 544, 8, torch.float32).build()
-    out = torch.empty(1, 544, device=G.DEV)
+    big = G.PagedSequences([20], [2], 1, 1, 544, 8, torch.float32).build()
+    out = torch.empty(2, 544, device=G.DEV)
+    K.attention_simple(big.q_dev, 544, out, big.positions, big.tok_row, big.table, big.kpool, big.vpool, 1, 1, 544,
+                       8, big.num_pages, None, 0.05, K.new_error_word(G.DEV))
+    assert float((out.double().cpu() - big.reference(0.05).reshape(2, 544)).abs().max()) < 1e-5
+    huge = G.PagedSequences([20], [1], 1, 1, 1040, 8, torch.float32).build()
+    out = torch.empty(1, 1040, device=G.DEV)
     with pytest.raises(Exception, match="does not take these sizes"):
-        K.attention_simple(big.q_dev, 544, out, big.positions, big.tok_row, big.table, big.kpool, big.vpool, 1, 1, 544,
-                           8, big.num_pages, None, 1.0, K.new_error_word(G.DEV))
+        K.attention_simple(huge.q_dev, 1040, out, huge.positions, huge.tok_row, huge.table, huge.kpool, huge.vpool, 1, 1, 1040,
+                           8, huge.num_pages, None, 1.0, K.new_error_word(G.DEV))
 
 
 # ------------------------------------------------------------------------------------------------ sampling
