@@ -531,6 +531,34 @@ def test_layer_by_layer(tmp_path_factory, name):
         S.assert_close(got, want, "float32", f"{name}: the first {n} layers ({cfg.layers[n - 1].type} last)")
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_configurations_drawn_at_random(tmp_path_factory, seed):
+    """2 to 5 layers of any kind in any order with sizes drawn from small sets: a whole prompt, then the same prompt in
+    portions and single tokens through a pool of four pages' slack, float32 against the plain model and bfloat16 against
+    float32's bars for bfloat16"""
+    import os
+    from mashbox_b200.engine.replay import make_runner
+    from mashbox_b200.weights.random_init import write_model_folder
+    from tests.plain.llama import read_model
+    cfg = S.random_config(seed)
+    page = (4, 8, 16, 5)[seed % 4]
+    tmp = tmp_path_factory.mktemp("r")
+    rng = np.random.default_rng(seed)
+    p = rng.integers(0, cfg.vocab, 75).tolist()
+    for dtype in DTYPES:
+        d = os.path.join(str(tmp), dtype)
+        write_model_folder(d, cfg, 500 + seed, dtype=TD[dtype], std=cfg.width ** -0.5, norm_std=0.1, std_by_name=S.STD_BY_NAME)
+        c, W = read_model(d)
+        want = plain.forward(c, W, p).numpy()
+        runner = make_runner(d, dtype, 128, page_size=page)
+        whole = replay(runner, cut_steps("a", p, [len(p)]))[0]
+        S.assert_close(whole, want, dtype, f"random configuration {seed}: {[l.type for l in cfg.layers]}, whole")
+        cuts = [33, 2, 1, 17, 1, 1, 20]
+        out = replay(runner, cut_steps("b", p, cuts))
+        S.assert_close(np.concatenate([out[i] for i in range(len(cuts))]), want, dtype, f"random configuration {seed}, in portions")
+        runner.cache.check()
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_whole_prompts_and_first_tokens(tmp_path_factory, name, dtype):
     folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 320)
