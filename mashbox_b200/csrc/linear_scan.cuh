@@ -134,6 +134,70 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         else asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group %0;\n" ::"n"(DR_STAGES - 1));
         __syncthreads();
+        if (MODE != 0) {
+            // No delta step: nothing of a token's read-out feeds the next token, so the read-outs of a whole stage of tokens are met
+            // together -- eight independent chains of shuffles in flight instead of one after every token.  The arithmetic
+            // of a token is what it is in the other branch, in the same order.
+            constexpr int TB = 8;
+            for (int tt0 = 0; tt0 < nb; tt0 += TB) {
+                float accs[TB][CPT];
+#pragma unroll
+                for (int j = 0; j < TB; j++) {
+                    const int tt = tt0 + j;
+#pragma unroll
+                    for (int c = 0; c < CPT; c++) accs[j][c] = 0.0f;
+                    if (tt < nb) {                      // the same for every thread of the block
+                        uint64_t asum[CPT][2];
+                        const uint64_t zero2 = dr_pack2(0.0f, 0.0f);
+#pragma unroll
+                        for (int c = 0; c < CPT; c++) asum[c][0] = asum[c][1] = zero2;
+#pragma unroll
+                        for (int r4 = 0; r4 < R4; r4++) {
+                            float4 gg;
+                            if (MODE == 2) gg.x = gg.y = gg.z = gg.w = sb[buf][tt];
+                            else gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * LANES + lane * 4]);
+                            const float4 kk = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * LANES + lane * 4]);
+                            const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * LANES + lane * 4]);
+                            const uint64_t g01 = dr_pack2(gg.x, gg.y), g23 = dr_pack2(gg.z, gg.w);
+                            const uint64_t k01 = dr_pack2(kk.x, kk.y), k23 = dr_pack2(kk.z, kk.w);
+                            const uint64_t q01 = dr_pack2(qq.x, qq.y), q23 = dr_pack2(qq.z, qq.w);
+#pragma unroll
+                            for (int c = 0; c < CPT; c++) {
+                                const float uc = sv[buf][tt][cg * CPT + c];
+                                const uint64_t u2 = dr_pack2(uc, uc);
+                                st[c][r4 * 2] = dr_fma2(st[c][r4 * 2], g01, zero2);       // the decay: a product, rounded once
+                                st[c][r4 * 2 + 1] = dr_fma2(st[c][r4 * 2 + 1], g23, zero2);
+                                st[c][r4 * 2] = dr_fma2(k01, u2, st[c][r4 * 2]);
+                                st[c][r4 * 2 + 1] = dr_fma2(k23, u2, st[c][r4 * 2 + 1]);
+                                asum[c][0] = dr_fma2(st[c][r4 * 2], q01, asum[c][0]);
+                                asum[c][1] = dr_fma2(st[c][r4 * 2 + 1], q23, asum[c][1]);
+                            }
+                        }
+#pragma unroll
+                        for (int c = 0; c < CPT; c++) {
+                            float a0, a1, a2, a3;
+                            dr_unpack2(asum[c][0], a0, a1);
+                            dr_unpack2(asum[c][1], a2, a3);
+                            accs[j][c] = (a0 + a1) + (a2 + a3);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m = 1; m < LANES; m <<= 1)
+#pragma unroll
+                    for (int j = 0; j < TB; j++)
+#pragma unroll
+                        for (int c = 0; c < CPT; c++) accs[j][c] += __shfl_xor_sync(0xffffffffu, accs[j][c], m);
+                if (lane == 0) {
+#pragma unroll
+                    for (int j = 0; j < TB; j++)
+#pragma unroll
+                        for (int c = 0; c < CPT; c++)
+                            if (tt0 + j < nb && colA + c < vdim)
+                                o[((size_t)(a + t0 + tt0 + j) * H + h) * vdim + colA + c] = accs[j][c];
+                }
+            }
+        } else
 #pragma unroll 2
         for (int tt = 0; tt < nb; tt++) {
             // a value of q, k, g read from shared memory serves the thread's CPT columns; the arithmetic runs on pairs
