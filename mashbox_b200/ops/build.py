@@ -44,6 +44,10 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "stream": ("stream.cu", []),                                       # Dynamic Tanh, depth averaging, two normed outputs
     "retention": ("retention.cu", []),                                 # linear attention with a fixed decay per head
     "attention_sigmoid": ("attention_sigmoid.cu", []),                 # attention whose weights are sigmoids
+    # the general attention (keys and values of their own widths, cap, sinks, gates): one library per pair of widths,
+    # registered when a model brings the pair (ops._general_mma_library); these two are always built
+    "attention_general_mma_128_64": ("attention_general_mma.cu", ["-DGA_DK=128", "-DGA_DV=64"]),
+    "attention_general_mma_192_128": ("attention_general_mma.cu", ["-DGA_DK=192", "-DGA_DV=128"]),
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),
